@@ -1,0 +1,342 @@
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|...] [--impl b200|reference]
+
+One step = one pass of the hot path (activation pre-pass + W4 GEMM with fused epilogue)
+over one batch of seeded synthetic input.  The default workload is the configuration the
+headline metric is quoted on: a single W4A4+RHT linear, M=2048, K=3072, N=3072, group-128
+fp16 weight scales, per-token int4 activations, 128-point randomized Hadamard transform.
+Prints ONE JSON line (rank 0).  Multi-GPU runs shard tokens (M) across ranks with replicated
+weights and no collective: every rank runs the per-GPU workload, so scaling is "weak".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (M, K, N, activation bits, rotate)
+    "c1": (256, 1024, 1024, 8, False),
+    "c2": (2048, 3072, 3072, 4, True),
+    "c2_a8": (2048, 3072, 3072, 8, False),
+    "m4096_ffn_up": (4096, 3072, 12288, 4, True),
+    "m4096_ffn_down": (4096, 12288, 3072, 4, True),
+    "m16384": (16384, 3072, 3072, 4, True),
+}
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(m, k, n, rotate):
+    """bf16 x + int4 w + fp16 group scales + bias + bf16 out (+ fp32 signs)."""
+    return 2 * m * k + n * k // 2 + 2 * n * (k // 128) + 2 * n + 2 * m * n + (4 * k if rotate else 0)
+
+
+def load_oracle():
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import steerquant_oracle
+    return steerquant_oracle
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every 100 ms."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._halt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # no NVML: report empty clocks rather than fail the bench
+            self.nvml = None
+
+    def run(self):
+        while self.nvml is not None and not self._halt.is_set():
+            try:
+                self.samples.append(self.nvml.nvmlDeviceGetClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+                mask = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._halt.wait(0.1)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=2)
+        mid = sorted(self.samples)[len(self.samples) // 2] if self.samples else None
+        return {"sm_mhz": mid, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_forward_factory(oracle, case):
+    """The reference's CPU arithmetic for this scheme: fake-quantize the (rotated) activation,
+    one bf16 F.linear against the dequantized weight (runtime.py:155-175)."""
+    def run():
+        return oracle.token_module_forward(case["x"], case["qweight"], case["weight_scales"], case["bias"],
+                                           abits=case["abits"], signs=case["signs"])
+    return run
+
+
+def time_cpu(run, seconds_budget=20.0, min_repeats=3, max_repeats=30):
+    run()  # warm-up
+    times = []
+    start = time.perf_counter()
+    while len(times) < min_repeats or (time.perf_counter() - start < seconds_budget and len(times) < max_repeats):
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2], len(times)
+
+
+def run_reference(args, m, k, n, abits, rotate):
+    """--impl reference: the CPU port of the reference's fake-quant path on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle = load_oracle()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    case = oracle.prepare_token_linear(m, k, n, abits=abits, seed=0)
+    run = cpu_forward_factory(oracle, case)
+    for _ in range(max(1, min(args.warmup, 2))):
+        run()
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    elapsed = time.perf_counter() - t0
+    tops = 2.0 * m * n * k * steps / elapsed / 1e12
+    line = {
+        "impl": "reference", "metric": "W4A%d%s GEMM int-TOPS" % (abits, "+RHT" if rotate else ""),
+        "value": tops, "unit": "TOPS", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 (CPU fake-quant)", "data": "synthetic",
+        "config": {"workload": args.workload, "M": m, "K": k, "N": n, "abits": abits, "rht": rotate},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
+                         "sample": "%d full passes of the workload" % steps},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def measure_int8_peak(device):
+    """Dense int8 tensor-core peak the way the bf16 peak was measured: torch._int_mm 8192^3, best of 10."""
+    a = torch.randint(-8, 8, (8192, 8192), device=device, dtype=torch.int8)
+    b = torch.randint(-8, 8, (8192, 8192), device=device, dtype=torch.int8).t()
+    for _ in range(3):
+        torch._int_mm(a, b)
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch._int_mm(a, b)
+        e1.record()
+        e1.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return 2.0 * 8192 ** 3 / (best * 1e-3) / 1e12
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    m, k, n, abits, rotate = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference(args, m, k, n, abits, rotate)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    distributed = world > 1
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback.")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if distributed:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    import __graft_entry__ as entry
+    entry.load_package()
+    from fastwamjoint_quantization_b200 import native
+
+    oracle = load_oracle()
+    # rank r of a sharded job holds rows [r*M, (r+1)*M) of a global batch of world*M tokens: same
+    # weights (seed 0), its own activations (x seed = rank)
+    case = oracle.prepare_token_linear(m, k, n, abits=abits, seed=0, x_seed=None if world == 1 else 1000 + rank)
+    packed_host = oracle.pack_signed_int4(case["qweight"])
+    signs = None if case["signs"] is None else case["signs"].to(device)
+
+    # rotating input sets so every step reads x and W from HBM, not from L2
+    set_bytes = algorithmic_bytes(m, k, n, rotate)
+    nsets = max(2, -(-2 * L2_BYTES // set_bytes))
+    xs, packs, wss = [], [], []
+    for i in range(nsets):
+        xs.append((case["x"].float() * (1.0 + 0.001 * i)).to(torch.bfloat16).to(device))
+        packs.append(packed_host.to(device).clone())
+        wss.append(case["weight_scales"].to(device).clone())
+    bias = case["bias"].to(device)
+
+    def step(i):
+        j = i % nsets
+        return native.linear(xs[j], packs[j], wss[j], bias, abits=abits, mode="token", signs=signs)
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # correctness of what is being timed (small slice, against the oracle)
+    out0 = step(0)
+    rows = min(m, 64)
+    want = oracle.linear_token(case["x"][:rows], case["qweight"], case["weight_scales"], case["bias"], abits=abits,
+                               signs=case["signs"], want_accumulators=False)["out"]
+    err = ((out0[:rows].cpu().float() - want.float()).norm() / want.float().norm()).item()
+    if not err < 1e-2:
+        raise SystemExit(f"bench output differs from the oracle: relative Frobenius error {err}")
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+
+    # dominant kernel alone (the GEMM), same rotation, for the roofline
+    pre = [native.prepass(xs[j], abits=abits, mode="token", signs=signs) for j in range(nsets)]
+    for i in range(3):
+        native.gemm(pre[i % nsets][0], packs[i % nsets], wss[i % nsets], pre[i % nsets][1], bias, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for i in range(args.steps):
+        j = i % nsets
+        native.gemm(pre[j][0], packs[j], wss[j], pre[j][1], bias, out_dtype=torch.bfloat16)
+    g1.record()
+    torch.cuda.synchronize()
+    gemm_ms = g0.elapsed_time(g1) / args.steps
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for i in range(args.steps):
+        native.prepass(xs[i % nsets], abits=abits, mode="token", signs=signs)
+    p1.record()
+    torch.cuda.synchronize()
+    prepass_ms = p0.elapsed_time(p1) / args.steps
+
+    # end to end through the public call with HOST buffers: pinned x -> device, linear, result -> pinned host
+    x_host = case["x"].pin_memory()
+    out_host = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty_like(xs[0])
+    e2e_steps = max(5, min(args.steps, 50))
+    for i in range(3):
+        x_dev.copy_(x_host, non_blocking=True)
+        out_host.copy_(native.linear(x_dev, packs[0], wss[0], bias, abits=abits, mode="token", signs=signs), non_blocking=True)
+    barrier()
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h0.record()
+    for i in range(e2e_steps):
+        j = i % nsets
+        x_dev.copy_(x_host, non_blocking=True)
+        out_host.copy_(native.linear(x_dev, packs[j], wss[j], bias, abits=abits, mode="token", signs=signs), non_blocking=True)
+    h1.record()
+    barrier()
+    e2e_ms = h0.elapsed_time(h1)
+    clocks = sampler.stop()
+    status = native.device_status()
+    if status != 0:
+        raise SystemExit(f"a kernel gave up a bounded wait: device status {status}")
+
+    if distributed:
+        t = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms = t.tolist()
+
+    ops_per_step = 2.0 * m * n * k
+    tops = world * ops_per_step * args.steps / (elapsed_ms * 1e-3) / 1e12
+    e2e_tops = world * ops_per_step * e2e_steps / (e2e_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks = {}
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        if peaks_file.exists():
+            peaks = json.loads(peaks_file.read_text())
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        try:
+            int8_peak = measure_int8_peak(device)
+            int8_source = "torch._int_mm 8192^3 best of 10, measured in this run (int8 is not in MEASURED_PEAKS.json)"
+        except Exception as exc:  # keep the bench line; say where the denominator came from
+            int8_peak = 2.0 * float(peaks.get("bf16_tflops", 1590.0))
+            int8_source = "2 x measured bf16 peak (torch._int_mm failed: %s)" % type(exc).__name__
+        gemm_tops = ops_per_step / (gemm_ms * 1e-3) / 1e12
+        t_compute = ops_per_step / (int8_peak * 1e12)
+        t_hbm = algorithmic_bytes(m, k, n, rotate) / (hbm_peak * 1e9)
+        if t_compute >= t_hbm:
+            roofline = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s",
+                        "frac": gemm_tops / int8_peak, "traffic": None,
+                        "peak_source": int8_source}
+        else:
+            gbs = algorithmic_bytes(m, k, n, rotate) / (gemm_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                        "traffic": None, "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"}
+        roofline["kernel"] = "sq_gemm_tc_kernel"
+        roofline["gemm_ms"] = gemm_ms
+        roofline["prepass_ms"] = prepass_ms
+        roofline["prepass_gbs"] = (2 * m * k + m * k + 4 * m) / (prepass_ms * 1e-3) / 1e9
+        line = {
+            "metric": "W4A%d%s GEMM int-TOPS" % (abits, "+RHT" if rotate else ""), "value": tops, "unit": "TOPS",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 x int4 -> int32", "data": "synthetic",
+            "config": {"workload": args.workload, "M_per_gpu": m, "K": k, "N": n, "abits": abits, "rht": rotate,
+                       "weight_scales": "fp16 group-128", "activation_scales": "per-token",
+                       "sharding": "tokens (M) across ranks, weights replicated, no collective",
+                       "l2": "rotating %d input sets (%.0f MB > 126 MB L2)" % (nsets, nsets * set_bytes / 1e6)},
+            "gpu_launches": 2 * args.steps,
+            "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms / e2e_steps},
+            "roofline": roofline, "clocks": clocks, "parity_rel_fro": err,
+        }
+        if not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            median, repeats = time_cpu(cpu_forward_factory(oracle, case))
+            line["cpu_baseline"] = {"value": ops_per_step / median / 1e12, "unit": "TOPS", "cores": cores, "kind": "port",
+                                    "sample": "median of %d full passes of the workload" % repeats}
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

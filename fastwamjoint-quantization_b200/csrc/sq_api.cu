@@ -1,0 +1,247 @@
+// extern "C" surface of libsq_b200.so, argument validation, the device status word and the
+// CUDA-core cross-check GEMM.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <type_traits>
+
+#include "sq_internal.h"
+
+namespace sq {
+
+// ------------------------------------------------------------------ device status word
+__device__ int g_device_status = 0;
+
+int* device_status_word() {
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_device_status) == cudaSuccess) cached[dev] = static_cast<int*>(ptr);
+  }
+  return cached[dev];
+}
+
+// ------------------------------------------------------------------ validation
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate_gemm(const GemmArgs& a) {
+  if (a.codes == nullptr || a.w_packed == nullptr || a.w_scales == nullptr || a.row_scales == nullptr || a.out == nullptr)
+    return SQ_ERR_NULL;
+  if (a.codes_layout != SQ_CODES_NATURAL && a.codes_layout != SQ_CODES_EVEN_ODD) return SQ_ERR_ENUM;
+  if (a.wscale_mode != SQ_WSCALE_CHANNEL_F32 && a.wscale_mode != SQ_WSCALE_GROUP_F16) return SQ_ERR_ENUM;
+  if (a.out_dtype != SQ_BF16 && a.out_dtype != SQ_FP16) return SQ_ERR_ENUM;
+  if (a.M < 0 || a.N <= 0 || a.K <= 0) return SQ_ERR_SHAPE;
+  if (a.K % 32 != 0 || a.N % 8 != 0 || a.K < 128) return SQ_ERR_SHAPE;
+  if (a.wscale_mode == SQ_WSCALE_GROUP_F16 && a.K % 128 != 0) return SQ_ERR_SHAPE;
+  if (a.M > (int64_t{1} << 30) || a.N > (int64_t{1} << 30) || a.K > 131072) return SQ_ERR_SHAPE;
+  if (!aligned16(a.codes) || !aligned16(a.w_packed) || !aligned16(a.out)) return SQ_ERR_SHAPE;
+  return SQ_OK;
+}
+
+// ------------------------------------------------------------------ cross-check GEMM (CUDA cores)
+// One thread per output element.  fp32 steps are separate multiplies and adds in the oracle's order,
+// so this kernel matches the CPU oracle bit for bit.
+template <typename OutT>
+__global__ void sq_gemm_check_kernel(const int8_t* __restrict__ codes, int even_odd, const uint8_t* __restrict__ packed,
+                                     const void* __restrict__ w_scales, int group_mode, const float* __restrict__ row_scales,
+                                     const OutT* __restrict__ bias, OutT* __restrict__ out, int64_t M, int64_t N, int64_t K,
+                                     int32_t* __restrict__ acc_dump) {
+  const int64_t n = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t m = blockIdx.y;
+  if (n >= N || m >= M) return;
+  const int8_t* a = codes + m * K;
+  const uint8_t* w = packed + n * (K / 2);
+  const int groups = group_mode ? static_cast<int>(K / 128) : 1;
+  const int64_t group_len = group_mode ? 128 : K;
+  float total = 0.0f;
+  int32_t acc_all = 0;
+  for (int g = 0; g < groups; ++g) {
+    int32_t acc = 0;
+    for (int64_t k8 = g * group_len; k8 < (g + 1) * group_len; k8 += 8) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint8_t byte = w[(k8 >> 1) + j];
+        const int lo = (static_cast<int>(byte & 0xF) ^ 8) - 8;  // k8 + 2j
+        const int hi = (static_cast<int>(byte >> 4) ^ 8) - 8;   // k8 + 2j + 1
+        const int a_lo = even_odd ? a[k8 + j] : a[k8 + 2 * j];
+        const int a_hi = even_odd ? a[k8 + 4 + j] : a[k8 + 2 * j + 1];
+        acc += a_lo * lo + a_hi * hi;
+      }
+    }
+    if (acc_dump != nullptr) acc_dump[(m * N + n) * groups + g] = acc;
+    if (group_mode) {
+      const float s = __half2float(static_cast<const __half*>(w_scales)[n * groups + g]);
+      total = __fadd_rn(total, __fmul_rn(static_cast<float>(acc), s));
+    } else {
+      acc_all = acc;
+    }
+  }
+  float y;
+  if (group_mode) {
+    y = __fmul_rn(total, row_scales[m]);
+  } else {
+    y = __fmul_rn(__fmul_rn(static_cast<float>(acc_all), row_scales[m]), static_cast<const float*>(w_scales)[n]);
+  }
+  if (bias != nullptr) {
+    float b;
+    if constexpr (std::is_same<OutT, __half>::value) b = __half2float(bias[n]);
+    else b = __bfloat162float(bias[n]);
+    y = __fadd_rn(y, b);
+  }
+  if constexpr (std::is_same<OutT, __half>::value) out[m * N + n] = __float2half_rn(y);
+  else out[m * N + n] = __float2bfloat16_rn(y);
+}
+
+int launch_gemm_check(const GemmArgs& a, cudaStream_t stream) {
+  int v = validate_gemm(a);
+  if (v != SQ_OK) return v;
+  if (a.M == 0) return SQ_OK;
+  if (a.M > 65535) return SQ_ERR_SHAPE;
+  const dim3 block(128);
+  const dim3 grid(static_cast<unsigned>((a.N + 127) / 128), static_cast<unsigned>(a.M));
+  const int eo = a.codes_layout == SQ_CODES_EVEN_ODD;
+  const int gm = a.wscale_mode == SQ_WSCALE_GROUP_F16;
+  if (a.out_dtype == SQ_BF16) {
+    sq_gemm_check_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(
+        a.codes, eo, a.w_packed, a.w_scales, gm, a.row_scales, static_cast<const __nv_bfloat16*>(a.bias),
+        static_cast<__nv_bfloat16*>(a.out), a.M, a.N, a.K, a.acc_dump);
+  } else {
+    sq_gemm_check_kernel<__half><<<grid, block, 0, stream>>>(
+        a.codes, eo, a.w_packed, a.w_scales, gm, a.row_scales, static_cast<const __half*>(a.bias),
+        static_cast<__half*>(a.out), a.M, a.N, a.K, a.acc_dump);
+  }
+  cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
+}
+
+static size_t round256(size_t v) { return (v + 255u) & ~static_cast<size_t>(255u); }
+
+}  // namespace sq
+
+// ====================================================================== C ABI
+extern "C" {
+#pragma GCC visibility push(default)
+
+int sq_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
+               const float* signs, int rht_block, const float* act_scale, const float* gains, int64_t span,
+               int64_t streams, int64_t seq_tokens, int codes_layout, int pack_int4, void* codes, float* row_scales,
+               void* stream) {
+  return sq::launch_prepass(x, x_dtype, rows, K, abits, mode, inv_d, signs, rht_block, act_scale, gains, span, streams,
+                            seq_tokens, codes_layout, pack_int4, codes, row_scales, static_cast<cudaStream_t>(stream));
+}
+
+static sq::GemmArgs make_args(const void* codes, int codes_layout, const void* w_packed, const void* w_scales,
+                              int wscale_mode, const float* row_scales, const void* bias, void* out, int out_dtype,
+                              int64_t M, int64_t N, int64_t K, int32_t* acc_dump) {
+  sq::GemmArgs a;
+  a.codes = static_cast<const int8_t*>(codes);
+  a.codes_layout = codes_layout;
+  a.w_packed = static_cast<const uint8_t*>(w_packed);
+  a.w_scales = w_scales;
+  a.wscale_mode = wscale_mode;
+  a.row_scales = row_scales;
+  a.bias = bias;
+  a.out = out;
+  a.out_dtype = out_dtype;
+  a.M = M; a.N = N; a.K = K;
+  a.acc_dump = acc_dump;
+  return a;
+}
+
+int sq_gemm(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+            const float* row_scales, const void* bias, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+            int32_t* acc_dump, void* stream) {
+  return sq::launch_gemm_tc(make_args(codes, codes_layout, w_packed, w_scales, wscale_mode, row_scales, bias, out,
+                                      out_dtype, M, N, K, acc_dump),
+                            static_cast<cudaStream_t>(stream));
+}
+
+int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+                  const float* row_scales, const void* bias, void* out, int out_dtype, int64_t M, int64_t N,
+                  int64_t K, int32_t* acc_dump, void* stream) {
+  return sq::launch_gemm_check(make_args(codes, codes_layout, w_packed, w_scales, wscale_mode, row_scales, bias, out,
+                                         out_dtype, M, N, K, acc_dump),
+                               static_cast<cudaStream_t>(stream));
+}
+
+size_t sq_workspace_bytes(int64_t M, int64_t K) {
+  if (M < 0 || K < 0) return 0;
+  return sq::round256(static_cast<size_t>(M) * static_cast<size_t>(K)) + sq::round256(static_cast<size_t>(M) * 4u);
+}
+
+int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode, const float* inv_d,
+              const float* signs, int rht_block, const float* act_scales, const float* gains, int64_t calls,
+              int64_t call, int64_t span, int64_t streams, int64_t seq_tokens, const void* w_packed,
+              const void* w_scales, int wscale_mode, const void* bias, void* out, void* workspace,
+              size_t workspace_bytes, void* stream) {
+  if (workspace == nullptr && rows > 0) return SQ_ERR_NULL;
+  if (workspace_bytes < sq_workspace_bytes(rows, K)) return SQ_ERR_WORKSPACE;
+  const float* act_scale = nullptr;
+  const float* gain_row = nullptr;
+  if (mode == SQ_ACT_STATIC) {
+    if (act_scales == nullptr || gains == nullptr) return SQ_ERR_NULL;
+    if (calls <= 0 || call < 0 || call >= calls) return SQ_ERR_INDEX;
+    if (streams <= 0) return SQ_ERR_SHAPE;
+    act_scale = act_scales + call;
+    gain_row = gains + call * streams;
+  }
+  int8_t* codes = static_cast<int8_t*>(workspace);
+  float* row_scales = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
+                                               sq::round256(static_cast<size_t>(rows) * static_cast<size_t>(K)));
+  // validate the GEMM half before launching anything, so a rejected call leaves no work on the stream
+  sq::GemmArgs a = make_args(codes, SQ_CODES_EVEN_ODD, w_packed, w_scales, wscale_mode, row_scales, bias, out, x_dtype,
+                             rows, N, K, nullptr);
+  if (rows > 0) {
+    int v = sq::validate_gemm(a);
+    if (v != SQ_OK) return v;
+  }
+  int status = sq::launch_prepass(x, x_dtype, rows, K, abits, mode, inv_d, signs, rht_block, act_scale, gain_row, span,
+                                  streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
+                                  static_cast<cudaStream_t>(stream));
+  if (status != SQ_OK) return status;
+  return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
+}
+
+int sq_device_status(void) {
+  int* word = sq::device_status_word();
+  if (word == nullptr) return SQ_ERR_DRIVER;
+  int value = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return SQ_ERR_DRIVER;
+  if (cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return SQ_ERR_DRIVER;
+  if (value != 0) {
+    int zero = 0;
+    cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return value;
+}
+
+const char* sq_status_string(int status) {
+  switch (status) {
+    case SQ_OK: return "ok";
+    case SQ_ERR_NULL: return "a required pointer is null";
+    case SQ_ERR_SHAPE: return "unsupported shape or alignment";
+    case SQ_ERR_ENUM: return "enum argument out of range";
+    case SQ_ERR_INDEX: return "schedule index out of range";
+    case SQ_ERR_DRIVER: return "CUDA driver call failed";
+    case SQ_ERR_WORKSPACE: return "workspace too small";
+    case SQ_ERR_DEVICE_WAIT: return "a kernel gave up a bounded wait";
+    case 9001: return "device: TMA producer timed out waiting for a free stage";
+    case 9002: return "device: MMA warp timed out waiting for a free accumulator";
+    case 9003: return "device: MMA warp timed out waiting for operands";
+    case 9004: return "device: converter warp timed out waiting for packed weights";
+    case 9005: return "device: drain warp timed out waiting for an accumulator";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown status";
+}
+
+const char* sq_version(void) { return "sq_b200 sm_100a"; }
+
+#pragma GCC visibility pop
+}  // extern "C"

@@ -1,0 +1,508 @@
+// W4A8 / W4A4 GEMM on the 5th-generation tensor cores: out[m, n] = sum_k a[m, k] * w[n, k].
+//
+// The MMA runs "weights as rows": the UMMA M dimension (TMEM lanes) is 128 output channels,
+// the UMMA N dimension (TMEM columns) is up to 256 tokens.  A TMEM lane therefore belongs to ONE
+// output channel, so the per-group weight scale is a per-thread scalar when the accumulator is
+// drained, and small token counts map to a small UMMA N instead of a wasted 128-row tile.
+//
+// Per CTA (persistent over tiles, 512 threads = 4 warpgroups):
+//   warp 0        TMA producer: per 128-K block one box of packed int4 weights [128 ch x 64 B] and one
+//                 box of int8 activation codes [TOK x 128 B, 128-byte swizzle]
+//   warp 1        allocates TMEM, issues tcgen05.mma.kind::i8 (4 x K=32 per block), commits to mbarriers
+//   warps 4-7     unpack int4 -> int8 from the packed stage into the canonical K-major 128B-swizzled
+//                 operand tile (nibble v becomes the int8 value 16 v; the factor 1/16 is exact and is
+//                 folded into the scale)
+//   warps 8-15    drain: tcgen05.ld the int32 accumulator of one weight group, convert, multiply by
+//                 the group scale, add into fp32 sums in registers; after the last group apply the row
+//                 scale and bias and store bf16/fp16
+// Two TMEM accumulators of TOK columns alternate, so the MMAs of group g+1 overlap the drain of g.
+//
+// Every mbarrier wait is time-bounded (see sq_ptx.cuh); a wait that gives up sets the CTA's abort
+// flag and the device status word, all roles leave their loops, TMEM is released, the kernel returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+
+#include "sq_internal.h"
+#include "sq_ptx.cuh"
+
+namespace sq {
+
+namespace {
+
+constexpr int kBlockCh = 128;  // output channels per tile = UMMA M = TMEM lanes
+constexpr int kBlockK = 128;   // int8 K elements per stage = one swizzle row = one weight group
+constexpr int kUmmaK = 32;     // K of one kind::i8 instruction
+constexpr int kThreads = 512;
+constexpr uint32_t kPackedBytes = kBlockCh * kBlockK / 2;  // 8 KiB
+constexpr uint32_t kWBytes = kBlockCh * kBlockK;           // 16 KiB
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+constexpr uint32_t kMagicBits = 0x4B400000u;               // float 12582912 = 1.5 * 2^23
+constexpr float kMagicFloat = 12582912.0f;
+
+constexpr int kNumConverterWarps = 4;
+constexpr int kNumDrainWarps = 8;
+
+__host__ __device__ constexpr int stages_for(int tok) {
+  // shared memory per stage: unpacked weights + codes + packed weights
+  return tok == 256 ? 4 : tok == 128 ? 5 : tok == 64 ? 7 : 8;
+}
+__host__ __device__ constexpr uint32_t stage_bytes(int tok) { return kWBytes + tok * kBlockK + kPackedBytes; }
+__host__ __device__ constexpr uint32_t smem_bytes_for(int tok) {
+  return stages_for(tok) * stage_bytes(tok) + 1024 /*alignment slack*/ + 512 /*barriers*/;
+}
+
+struct TcParams {
+  const void* w_scales;
+  const float* row_scales;
+  const void* bias;
+  void* out;
+  int32_t* acc_dump;
+  int* status;
+  int64_t M, N, K;
+  int ch_tiles, tok_tiles, k_blocks;
+  int out_dtype;
+};
+
+template <typename T>
+__device__ __forceinline__ T from_float(float f);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float f) { return __float2half_rn(f); }
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+
+template <int kRegs>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs)); }
+template <int kRegs>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs)); }
+
+__device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code) {
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+}
+
+// TOK    tokens per tile (TMEM columns per accumulator, rows of the codes box)
+// kGroup one accumulator per 128-K weight group (fp16 scales [N, K/128]); otherwise one per tile (fp32 [N])
+// kMagic group mode only: TMEM accumulators start at the bit pattern of 1.5 * 2^23, so the drained word
+//        re-read as a float is 12582912 + acc exactly and the int->float conversion is one subtraction
+// kEvenOdd codes are stored even-k-first inside each run of 8 (no byte interleave needed when unpacking)
+// kDump  also write the exact integer accumulators
+template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
+                  const TcParams p) {
+  static_assert(!kMagic || kGroup, "the magic-number drain needs |16 acc| < 2^22, true only per 128-K group");
+  constexpr int S = stages_for(TOK);
+  constexpr uint32_t kXBytes = TOK * kBlockK;
+  constexpr int kColsPerHalf = TOK / 2;           // columns drained by one warp of a lane quarter
+  constexpr int kChunk = 16;                      // columns per tcgen05.ld
+  constexpr int kChunks = kColsPerHalf / kChunk;  // per drain thread
+  constexpr uint32_t kTmemCols = 2 * TOK < 32 ? 32 : 2 * TOK;
+  static_assert(kColsPerHalf % kChunk == 0, "tile too narrow");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t w_ring = smem_base;                  // S x 16 KiB, unpacked weights (UMMA A)
+  const uint32_t x_ring = w_ring + S * kWBytes;       // S x TOK*128, codes (UMMA B)
+  const uint32_t p_ring = x_ring + S * kXBytes;       // S x 8 KiB, packed weights
+  const uint32_t bars = p_ring + S * kPackedBytes;    // mbarriers, 8 B each
+  const uint32_t bar_full = bars;                     // [S] TMA landed (tx bytes)
+  const uint32_t bar_wfull = bars + 8 * S;            // [S] converters wrote W[s]
+  const uint32_t bar_empty = bars + 16 * S;           // [S] MMAs reading stage s retired
+  const uint32_t bar_acc_full = bars + 24 * S;        // [2]
+  const uint32_t bar_acc_empty = bars + 24 * S + 16;  // [2]
+  const uint32_t tmem_slot = bars + 24 * S + 32;
+  const uint32_t abort_slot = tmem_slot + 4;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + (abort_slot - smem_base));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_wfull + 8 * s, kNumConverterWarps);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, kNumDrainWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_codes);
+    tma_prefetch_desc(&tmap_packed);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int num_tiles = p.ch_tiles * p.tok_tiles;
+  const int groups = kGroup ? p.k_blocks : 1;
+  const int blocks_per_group = kGroup ? 1 : p.k_blocks;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ control warpgroup
+    reg_dec<56>();
+    if (warp == 0 && lane == 0) {
+      // TMA producer
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int ch0 = (tile % p.ch_tiles) * kBlockCh;
+        const int tok0 = (tile / p.ch_tiles) * TOK;
+        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % S, phase = (it / S) & 1u;
+          if (!mbar_wait_bounded(bar_empty + 8 * s, phase ^ 1u, abort_flag, kWaitLimitNs)) {
+            report_timeout(p.status, abort_flag, 9001);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(bar_full + 8 * s, kXBytes + kPackedBytes);
+          tma_load_2d(p_ring + s * kPackedBytes, &tmap_packed, kb * (kBlockK / 2), ch0, bar_full + 8 * s);
+          tma_load_2d(x_ring + s * kXBytes, &tmap_codes, kb * kBlockK, tok0, bar_full + 8 * s);
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      // MMA issuer
+      uint32_t it = 0, git = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tok0 = (tile / p.ch_tiles) * TOK;
+        const int64_t left = p.M - tok0;
+        const int tok_count = left < TOK ? static_cast<int>(left) : TOK;
+        const uint32_t umma_n = static_cast<uint32_t>((tok_count + 15) & ~15);
+        const uint32_t idesc = umma_idesc_i8(kBlockCh, umma_n);
+        for (int g = 0; g < groups && ok; ++g, ++git) {
+          const uint32_t buf = git & 1u, aphase = (git >> 1) & 1u;
+          if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
+            report_timeout(p.status, abort_flag, 9002);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t tmem_d = tmem_base + buf * TOK;
+          for (int kb = 0; kb < blocks_per_group; ++kb, ++it) {
+            const uint32_t s = it % S, phase = (it / S) & 1u;
+            if (!mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs) ||
+                !mbar_wait_bounded(bar_wfull + 8 * s, phase, abort_flag, kWaitLimitNs)) {
+              report_timeout(p.status, abort_flag, 9003);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint64_t desc_a = umma_desc_k128(w_ring + s * kWBytes);
+            const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              const uint32_t accumulate = kMagic ? 1u : ((kb > 0 || k > 0) ? 1u : 0u);
+              // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in the (address >> 4) field
+              umma_i8(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
+            }
+            umma_commit(bar_empty + 8 * s);
+          }
+          if (ok) umma_commit(bar_acc_full + 8 * buf);
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ converter warpgroup
+    reg_dec<88>();
+    const int ctid = threadIdx.x - 128;  // 0..127
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        const uint32_t s = it % S, phase = (it / S) & 1u;
+        if (!mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs)) {
+          if (lane == 0) report_timeout(p.status, abort_flag, 9004);
+          ok = false;
+          break;
+        }
+        const uint32_t src = p_ring + s * kPackedBytes;
+        const uint32_t dst = w_ring + s * kWBytes;
+#pragma unroll
+        for (int u4 = 0; u4 < 4; ++u4) {
+          const int unit = u4 * 128 + ctid;  // 16 packed bytes = 32 k of one channel row
+          const int row = unit >> 2, c = unit & 3;
+          uint32_t w0, w1, w2, w3;
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                       : "r"(src + unit * 16));
+          uint32_t o[8];
+          const uint32_t win[4] = {w0, w1, w2, w3};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t lo = (win[i] << 4) & 0xF0F0F0F0u;  // 16 * nibble of even k, as int8
+            const uint32_t hi = win[i] & 0xF0F0F0F0u;         // 16 * nibble of odd k
+            if (kEvenOdd) {
+              o[2 * i] = lo;
+              o[2 * i + 1] = hi;
+            } else {
+              o[2 * i] = __byte_perm(lo, hi, 0x5140);      // k0 k1 k2 k3
+              o[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // k4 k5 k6 k7
+            }
+          }
+          const uint32_t row_base = dst + row * 128;
+          const uint32_t sw = static_cast<uint32_t>(row & 7);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (((2 * c) ^ sw) << 4)),
+                       "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (((2 * c + 1) ^ sw) << 4)),
+                       "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+        }
+        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_wfull + 8 * s);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ drain warpgroups
+    reg_inc<184>();
+    const int dwarp = warp - 8;           // 0..7
+    const int quarter = warp & 3;         // TMEM lane quarter this warp may address
+    const int half = dwarp >> 2;          // which half of the token columns
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int ch_in_tile = quarter * 32 + lane;
+
+    // hand both accumulators to the MMA warp (after writing the magic start value, if used)
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      if (kMagic) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          tmem_st_32x32b_x16_fill(tmem_base + lane_addr + b * TOK + half * kColsPerHalf + c * kChunk, kMagicBits);
+        tmem_wait_st();
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);
+    }
+
+    uint32_t git = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int ch0 = (tile % p.ch_tiles) * kBlockCh;
+      const int tok0 = (tile / p.ch_tiles) * TOK;
+      const int64_t left = p.M - tok0;
+      const int tok_count = left < TOK ? static_cast<int>(left) : TOK;
+      const int my_cols = min(max(tok_count - half * kColsPerHalf, 0), kColsPerHalf);  // real tokens in my half
+      const int64_t n = ch0 + ch_in_tile;
+      const bool n_ok = n < p.N;
+
+      float sums[kChunks * kChunk];
+#pragma unroll
+      for (int i = 0; i < kChunks * kChunk; ++i) sums[i] = 0.0f;
+
+      float scale_next = 0.0f;
+      if (kGroup) {
+        if (n_ok) scale_next = __half2float(__ldg(static_cast<const __half*>(p.w_scales) + n * groups)) * 0.0625f;
+      } else {
+        scale_next = 0.0625f;
+      }
+
+      for (int g = 0; g < groups && ok; ++g, ++git) {
+        const uint32_t buf = git & 1u, aphase = (git >> 1) & 1u;
+        const float scale = scale_next;
+        if (kGroup && g + 1 < groups && n_ok)
+          scale_next = __half2float(__ldg(static_cast<const __half*>(p.w_scales) + n * groups + g + 1)) * 0.0625f;
+        if (!mbar_wait_bounded(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
+          if (lane == 0) report_timeout(p.status, abort_flag, 9005);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + lane_addr + buf * TOK + half * kColsPerHalf;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          if (c * kChunk < my_cols) {  // warp-uniform
+            uint32_t r[kChunk];
+            tmem_ld_32x32b_x16(taddr + c * kChunk, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < kChunk; ++i) {
+              float value;
+              if (kMagic) {
+                value = __uint_as_float(r[i]) - kMagicFloat;
+              } else {
+                value = static_cast<float>(static_cast<int32_t>(r[i]));
+              }
+              sums[c * kChunk + i] = fmaf(value, scale, sums[c * kChunk + i]);
+              if (kDump) {
+                const int col = c * kChunk + i;
+                if (n_ok && col < my_cols) {
+                  const int64_t m = tok0 + half * kColsPerHalf + col;
+                  const int32_t acc16 = kMagic ? static_cast<int32_t>(r[i] - kMagicBits) : static_cast<int32_t>(r[i]);
+                  p.acc_dump[(m * p.N + n) * groups + g] = acc16 >> 4;
+                }
+              }
+            }
+            if (kMagic) tmem_st_32x32b_x16_fill(taddr + c * kChunk, kMagicBits);
+          }
+        }
+        if (kMagic) tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+      }
+      if (!ok) break;
+
+      // finalize: row scale, bias, cast, store.  Lanes hold consecutive channels -> 64 B per warp store.
+      if (n_ok) {
+        float wscale = 1.0f;
+        if (!kGroup) wscale = __ldg(static_cast<const float*>(p.w_scales) + n);
+        const bool has_bias = p.bias != nullptr;
+        const float bias = has_bias ? to_float<OutT>(__ldg(static_cast<const OutT*>(p.bias) + n)) : 0.0f;
+        OutT* out = static_cast<OutT*>(p.out);
+#pragma unroll
+        for (int i = 0; i < kChunks * kChunk; ++i) {
+          if (i < my_cols) {
+            const int64_t m = tok0 + half * kColsPerHalf + i;
+            const float rs = __ldg(p.row_scales + m);
+            float y;
+            if (kGroup) {
+              y = __fmul_rn(sums[i], rs);
+            } else {
+              y = __fmul_rn(__fmul_rn(sums[i], rs), wscale);
+            }
+            if (has_bias) y = __fadd_rn(y, bias);
+            out[m * p.N + n] = from_float<OutT>(y);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------- host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+// uint8 matrix [rows, row_bytes] -> box [box_rows, box_bytes]
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows,
+              uint32_t box_bytes, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_bytes, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT>
+int launch_variant(const GemmArgs& a, cudaStream_t stream) {
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kMagic, kEvenOdd, kDump, OutT>;
+  constexpr uint32_t smem = smem_bytes_for(TOK);
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev] = true;
+  }
+  CUtensorMap tmap_codes, tmap_packed;
+  if (!make_map(&tmap_codes, a.codes, static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.K), TOK, kBlockK,
+                CU_TENSOR_MAP_SWIZZLE_128B))
+    return SQ_ERR_DRIVER;
+  if (!make_map(&tmap_packed, a.w_packed, static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 2), kBlockCh,
+                kBlockK / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return SQ_ERR_DRIVER;
+  TcParams p;
+  p.w_scales = a.w_scales; p.row_scales = a.row_scales; p.bias = a.bias; p.out = a.out;
+  p.acc_dump = a.acc_dump; p.status = device_status_word();
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
+  p.tok_tiles = static_cast<int>((a.M + TOK - 1) / TOK);
+  p.k_blocks = static_cast<int>((a.K + kBlockK - 1) / kBlockK);
+  p.out_dtype = a.out_dtype;
+  const int tiles = p.ch_tiles * p.tok_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kThreads, smem, stream>>>(tmap_codes, tmap_packed, p);
+  cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
+}
+
+template <int TOK, bool kGroup, bool kMagic>
+int launch_tok(const GemmArgs& a, cudaStream_t stream) {
+  const bool eo = a.codes_layout == SQ_CODES_EVEN_ODD;
+  const bool dump = a.acc_dump != nullptr;
+  const bool bf16 = a.out_dtype == SQ_BF16;
+#define SQ_LAUNCH(EO, DUMP)                                                                          \
+  (bf16 ? launch_variant<TOK, kGroup, kMagic, EO, DUMP, __nv_bfloat16>(a, stream)                    \
+        : launch_variant<TOK, kGroup, kMagic, EO, DUMP, __half>(a, stream))
+  if (eo) return dump ? SQ_LAUNCH(true, true) : SQ_LAUNCH(true, false);
+  return dump ? SQ_LAUNCH(false, true) : SQ_LAUNCH(false, false);
+#undef SQ_LAUNCH
+}
+
+template <bool kGroup, bool kMagic>
+int launch_mode(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 32) return launch_tok<32, kGroup, kMagic>(a, stream);
+  if (a.M <= 64) return launch_tok<64, kGroup, kMagic>(a, stream);
+  if (a.M <= 128) return launch_tok<128, kGroup, kMagic>(a, stream);
+  return launch_tok<256, kGroup, kMagic>(a, stream);
+}
+
+}  // namespace
+
+int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
+  int v = validate_gemm(a);
+  if (v != SQ_OK) return v;
+  if (a.M == 0) return SQ_OK;
+  if (a.wscale_mode == SQ_WSCALE_GROUP_F16) return launch_mode<true, true>(a, stream);
+  return launch_mode<false, false>(a, stream);
+}
+
+}  // namespace sq

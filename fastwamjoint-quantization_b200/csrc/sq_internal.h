@@ -1,0 +1,39 @@
+// Internal launch functions shared by the translation units of libsq_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/sq_b200.h"
+
+namespace sq {
+
+int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
+                   const float* signs, int rht_block, const float* act_scale, const float* gains, int64_t span,
+                   int64_t streams, int64_t seq_tokens, int codes_layout, int pack_int4, void* codes,
+                   float* row_scales, cudaStream_t stream);
+
+struct GemmArgs {
+  const int8_t* codes;
+  int codes_layout;
+  const uint8_t* w_packed;
+  const void* w_scales;
+  int wscale_mode;
+  const float* row_scales;
+  const void* bias;
+  void* out;
+  int out_dtype;
+  int64_t M, N, K;
+  int32_t* acc_dump;
+};
+
+int validate_gemm(const GemmArgs& a);
+int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
+int launch_gemm_check(const GemmArgs& a, cudaStream_t stream);
+
+// Device-side status word (0 = fine).  Written by kernels that gave up a bounded wait.
+int* device_status_word();
+
+}  // namespace sq

@@ -1,0 +1,272 @@
+// Fused activation pre-pass: bf16/fp16 rows -> [sign flip + block Hadamard, rounded to the
+// input type] -> [1/D] -> per-token or scheduled scale -> int8 (or packed int4) codes + fp32
+// row scales.  One pass over global memory: each row lives in registers between the 128-bit
+// loads and the 64-bit code stores.
+//
+// Thread layout.  A row is covered by TPR threads (a power of two, 32..1024); thread t of the
+// row owns the 8-element vectors t, t + TPR, t + 2 TPR, ... (VPT of them), so a warp reads 512
+// contiguous bytes per load.  A rotation block of B elements is B/8 consecutive vectors, i.e.
+// B/8 consecutive lanes of one warp: three butterfly stages run inside the thread (strides 1,
+// 2, 4) and log2(B/8) stages run as __shfl_xor_sync exchanges (strides 8, 16, ...), which is the
+// stage order of the reference's CPU transform (rht.py:104-111), so the fp32 sums are the same.
+//
+// Arithmetic contract (what the CPU oracle does):
+//   token mode : s = max(amax / qmax, 1e-8);  code = clamp(rint(v / s))   (IEEE division, rint = half to even)
+//   static mode: f = gain / scale;            code = clamp(rint((v * inv_d) * f)),  row_scale = scale / gain
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+
+#include "sq_internal.h"
+
+namespace sq {
+
+template <typename T>
+struct Vec8;
+template <>
+struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void unpack(const uint4& raw, float (&v)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+  static __device__ __forceinline__ float round_trip(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+};
+template <>
+struct Vec8<__half> {
+  static __device__ __forceinline__ void unpack(const uint4& raw, float (&v)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      float2 f = __half22float2(h);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ float round_trip(float f) { return __half2float(__float2half_rn(f)); }
+};
+
+struct PrepassParams {
+  const void* x;
+  const float* inv_d;
+  const float* signs;
+  const float* act_scale;
+  const float* gains;
+  void* codes;
+  float* row_scales;
+  int64_t rows, K;
+  int64_t span, streams, seq_tokens;
+  int tpr_log2;        // threads per row = 1 << tpr_log2
+  int rht_lanes_log2;  // log2(block / 8): number of shuffle stages
+  float rht_norm;      // float(1 / sqrt(block))
+  int qmax;            // 127 or 7
+  int mode, codes_layout, pack_int4;
+};
+
+__device__ __forceinline__ int clamp_code(int q, int qmax) { return max(-qmax, min(qmax, q)); }
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(VPT > 4 ? 512 : 1024) sq_prepass_kernel(const PrepassParams p) {
+  const int tpr = 1 << p.tpr_log2;
+  const int t = threadIdx.x & (tpr - 1);
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> p.tpr_log2) + (threadIdx.x >> p.tpr_log2);
+  const bool row_ok = row < p.rows;
+  const int vectors = static_cast<int>(p.K >> 3);
+  const uint4* xrow = reinterpret_cast<const uint4*>(static_cast<const T*>(p.x) + (row_ok ? row : 0) * p.K);
+
+  float v[VPT][8];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int vec = j * tpr + t;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (row_ok && vec < vectors) raw = __ldg(xrow + vec);
+    Vec8<T>::unpack(raw, v[j]);
+  }
+
+  if (p.signs != nullptr) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int vec = j * tpr + t;
+      if (vec < vectors) {
+        const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.signs) + 2 * vec);
+        const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.signs) + 2 * vec + 1);
+        v[j][0] *= s0.x; v[j][1] *= s0.y; v[j][2] *= s0.z; v[j][3] *= s0.w;
+        v[j][4] *= s1.x; v[j][5] *= s1.y; v[j][6] *= s1.z; v[j][7] *= s1.w;
+      }
+      // strides 1, 2, 4 inside the thread
+#pragma unroll
+      for (int stride = 1; stride < 8; stride <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if ((i & stride) == 0) {
+            const float left = v[j][i], right = v[j][i + stride];
+            v[j][i] = left + right;
+            v[j][i + stride] = left - right;
+          }
+        }
+      }
+      // strides 8, 16, ... across lanes: the lane whose bit is clear holds "left"
+      for (int stage = 0; stage < p.rht_lanes_log2; ++stage) {
+        const int lane_bit = 1 << stage;
+        const bool is_right = (threadIdx.x & lane_bit) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[j][i], lane_bit);
+          v[j][i] = is_right ? (other - v[j][i]) : (v[j][i] + other);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[j][i] = Vec8<T>::round_trip(v[j][i] * p.rht_norm);
+    }
+  }
+
+  if (p.inv_d != nullptr) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int vec = j * tpr + t;
+      if (vec < vectors) {
+        const float4 d0 = __ldg(reinterpret_cast<const float4*>(p.inv_d) + 2 * vec);
+        const float4 d1 = __ldg(reinterpret_cast<const float4*>(p.inv_d) + 2 * vec + 1);
+        v[j][0] *= d0.x; v[j][1] *= d0.y; v[j][2] *= d0.z; v[j][3] *= d0.w;
+        v[j][4] *= d1.x; v[j][5] *= d1.y; v[j][6] *= d1.z; v[j][7] *= d1.w;
+      }
+    }
+  }
+
+  // scale: one number per row
+  float divisor = 1.0f;     // token mode: codes = v / divisor
+  float multiplier = 1.0f;  // static mode: codes = v * multiplier
+  if (p.mode == SQ_ACT_TOKEN) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+    if (tpr > 32) {
+      __shared__ float warp_max[32];
+      const int warp = threadIdx.x >> 5;
+      if ((threadIdx.x & 31) == 0) warp_max[warp] = amax;
+      __syncthreads();
+      const int warps_per_row = tpr >> 5;
+      const int first = (warp / warps_per_row) * warps_per_row;
+      amax = 0.0f;
+      for (int w = 0; w < warps_per_row; ++w) amax = fmaxf(amax, warp_max[first + w]);
+    }
+    divisor = fmaxf(__fdiv_rn(amax, static_cast<float>(p.qmax)), 1e-8f);
+    if (row_ok && t == 0) p.row_scales[row] = divisor;
+  } else {
+    int64_t stream;
+    if (p.span > 0) {
+      stream = (row / p.span) % p.streams;
+    } else {
+      stream = ((row % p.seq_tokens) < p.seq_tokens + p.span) ? 0 : 1;
+    }
+    const float scale = __ldg(p.act_scale);
+    const float gain = __ldg(p.gains + (row_ok ? stream : 0));
+    multiplier = __fdiv_rn(gain, scale);
+    if (row_ok && t == 0) p.row_scales[row] = __fdiv_rn(scale, gain);
+  }
+
+  if (!row_ok) return;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int vec = j * tpr + t;
+    if (vec >= vectors) continue;
+    int q[8];
+    if (p.mode == SQ_ACT_TOKEN) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = clamp_code(__float2int_rn(__fdiv_rn(v[j][i], divisor)), p.qmax);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = clamp_code(__float2int_rn(__fmul_rn(v[j][i], multiplier)), p.qmax);
+    }
+    if (p.pack_int4) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) word |= static_cast<uint32_t>(q[i] & 0xF) << (4 * i);
+      reinterpret_cast<uint32_t*>(p.codes)[row * vectors + vec] = word;
+    } else {
+      uint32_t lo, hi;
+      if (p.codes_layout == SQ_CODES_EVEN_ODD) {
+        lo = (q[0] & 0xFF) | ((q[2] & 0xFF) << 8) | ((q[4] & 0xFF) << 16) | (static_cast<uint32_t>(q[6] & 0xFF) << 24);
+        hi = (q[1] & 0xFF) | ((q[3] & 0xFF) << 8) | ((q[5] & 0xFF) << 16) | (static_cast<uint32_t>(q[7] & 0xFF) << 24);
+      } else {
+        lo = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | (static_cast<uint32_t>(q[3] & 0xFF) << 24);
+        hi = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | (static_cast<uint32_t>(q[7] & 0xFF) << 24);
+      }
+      reinterpret_cast<uint2*>(p.codes)[row * vectors + vec] = make_uint2(lo, hi);
+    }
+  }
+}
+
+template <typename T>
+static cudaError_t launch_for_type(const PrepassParams& p, int vpt, dim3 grid, dim3 block, cudaStream_t stream) {
+  switch (vpt) {
+    case 1: sq_prepass_kernel<T, 1><<<grid, block, 0, stream>>>(p); break;
+    case 2: sq_prepass_kernel<T, 2><<<grid, block, 0, stream>>>(p); break;
+    case 3: sq_prepass_kernel<T, 3><<<grid, block, 0, stream>>>(p); break;
+    case 4: sq_prepass_kernel<T, 4><<<grid, block, 0, stream>>>(p); break;
+    case 5: sq_prepass_kernel<T, 5><<<grid, block, 0, stream>>>(p); break;
+    default: sq_prepass_kernel<T, 6><<<grid, block, 0, stream>>>(p); break;
+  }
+  return cudaGetLastError();
+}
+
+int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
+                   const float* signs, int rht_block, const float* act_scale, const float* gains, int64_t span,
+                   int64_t streams, int64_t seq_tokens, int codes_layout, int pack_int4, void* codes,
+                   float* row_scales, cudaStream_t stream) {
+  if (x == nullptr || codes == nullptr || row_scales == nullptr) return SQ_ERR_NULL;
+  if (x_dtype != SQ_BF16 && x_dtype != SQ_FP16) return SQ_ERR_ENUM;
+  if (abits != 8 && abits != 4) return SQ_ERR_ENUM;
+  if (mode != SQ_ACT_STATIC && mode != SQ_ACT_TOKEN) return SQ_ERR_ENUM;
+  if (codes_layout != SQ_CODES_NATURAL && codes_layout != SQ_CODES_EVEN_ODD) return SQ_ERR_ENUM;
+  if (pack_int4 != 0 && (pack_int4 != 1 || abits != 4 || codes_layout != SQ_CODES_NATURAL)) return SQ_ERR_ENUM;
+  if (rows < 0 || K <= 0 || (K & 7) != 0 || K > 32768) return SQ_ERR_SHAPE;
+  if (rows == 0) return SQ_OK;
+  if (rows > (int64_t{1} << 31) - 1) return SQ_ERR_SHAPE;
+  int lanes_log2 = 0;
+  float norm = 1.0f;
+  if (signs != nullptr) {
+    if (rht_block < 8 || rht_block > 256 || (rht_block & (rht_block - 1)) != 0 || K % rht_block != 0) return SQ_ERR_SHAPE;
+    while ((8 << lanes_log2) < rht_block) ++lanes_log2;
+    norm = static_cast<float>(1.0 / std::sqrt(static_cast<double>(rht_block)));
+  }
+  if (mode == SQ_ACT_STATIC) {
+    if (act_scale == nullptr || gains == nullptr) return SQ_ERR_NULL;
+    if (streams <= 0 || span == 0) return SQ_ERR_SHAPE;
+    if (span < 0 && (seq_tokens <= 0 || -span >= seq_tokens || streams != 2)) return SQ_ERR_SHAPE;
+  }
+  // threads per row: smallest power of two >= 32 that leaves at most 6 vectors per thread
+  const int64_t vectors = K >> 3;
+  int tpr_log2 = 5;
+  while (((vectors + (int64_t{1} << tpr_log2) - 1) >> tpr_log2) > 6) ++tpr_log2;
+  const int tpr = 1 << tpr_log2;
+  const int vpt = static_cast<int>((vectors + tpr - 1) / tpr);
+  const int threads = tpr > 256 ? tpr : 256;
+  const int rows_per_cta = threads / tpr;
+
+  PrepassParams p;
+  p.x = x; p.inv_d = inv_d; p.signs = signs; p.act_scale = act_scale; p.gains = gains;
+  p.codes = codes; p.row_scales = row_scales; p.rows = rows; p.K = K;
+  p.span = span; p.streams = streams; p.seq_tokens = seq_tokens;
+  p.tpr_log2 = tpr_log2; p.rht_lanes_log2 = lanes_log2; p.rht_norm = norm;
+  p.qmax = abits == 8 ? 127 : 7; p.mode = mode; p.codes_layout = codes_layout; p.pack_int4 = pack_int4;
+
+  const dim3 grid(static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta));
+  const dim3 block(threads);
+  cudaError_t err = x_dtype == SQ_BF16 ? launch_for_type<__nv_bfloat16>(p, vpt, grid, block, stream)
+                                       : launch_for_type<__half>(p, vpt, grid, block, stream);
+  return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
+}
+
+}  // namespace sq

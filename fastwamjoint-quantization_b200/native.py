@@ -1,0 +1,104 @@
+"""Tensor-level wrappers over the C ABI: they allocate outputs and scratch with
+``torch.empty`` on the current device (so CUDA-graph capture uses PyTorch's
+graph-private pool, as the reference's ``torch::empty`` calls do,
+``kernels/w4a8/csrc/w4a8.cu:1358-1360``) and launch on the current stream."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16}
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: the B200 path has no CPU fallback.")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None, rht_block: int = 128,
+            act_scale=None, gains=None, span: int = 1, streams: int = 1, seq_tokens: int | None = None,
+            codes_layout: int = _lib.CODES_EVEN_ODD, pack_int4: bool = False):
+    """Run the fused activation pre-pass.  ``x`` is [..., tokens, K] bf16/fp16.
+    Returns ``(codes, row_scales)``: int8 [rows, K] (or uint8 [rows, K/2] when
+    ``pack_int4``) and fp32 [rows]."""
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    k = x.shape[-1]
+    rows = x.numel() // k
+    codes = torch.empty((rows, k // 2) if pack_int4 else (rows, k), device=x.device,
+                        dtype=torch.uint8 if pack_int4 else torch.int8)
+    row_scales = torch.empty((rows,), device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        status = _lib.load_library().sq_prepass(
+            x.data_ptr(), _DTYPES[x.dtype], rows, k, int(abits),
+            _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
+            _ptr(inverse), _ptr(signs), int(rht_block), _ptr(act_scale), _ptr(gains),
+            int(span), int(streams), int(seq_tokens if seq_tokens is not None else x.shape[-2]),
+            int(codes_layout), int(bool(pack_int4)), codes.data_ptr(), row_scales.data_ptr(), _stream())
+    _lib.check(status, "sq_prepass")
+    return codes, row_scales
+
+
+def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_scales: torch.Tensor, bias,
+         *, out_dtype: torch.dtype, codes_layout: int = _lib.CODES_EVEN_ODD, want_accumulators: bool = False,
+         check_kernel: bool = False):
+    """codes int8 [M, K] x packed uint8 [N, K/2] -> [M, N] in ``out_dtype``.
+    ``w_scales`` fp32 [N] selects the per-channel form, fp16 [N, K/128] the group form.
+    ``check_kernel`` runs the CUDA-core cross-check kernel instead of the tensor-core one (tests only)."""
+    _require_cuda(codes, "codes")
+    m, k = codes.shape
+    n = packed.shape[0]
+    group = w_scales.dtype == torch.float16
+    out = torch.empty((m, n), device=codes.device, dtype=out_dtype)
+    acc = None
+    if want_accumulators:
+        acc = torch.empty((m, n, k // 128 if group else 1), device=codes.device, dtype=torch.int32)
+    lib = _lib.load_library()
+    fn = lib.sq_gemm_check if check_kernel else lib.sq_gemm
+    with torch.cuda.device(codes.device):
+        status = fn(codes.data_ptr(), int(codes_layout), packed.data_ptr(), w_scales.data_ptr(),
+                    _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32, row_scales.data_ptr(), _ptr(bias),
+                    out.data_ptr(), _DTYPES[out_dtype], m, n, k, _ptr(acc), _stream())
+    _lib.check(status, "sq_gemm_check" if check_kernel else "sq_gemm")
+    return (out, acc) if want_accumulators else out
+
+
+def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, *, abits: int, mode: str,
+           inverse=None, signs=None, rht_block: int = 128, act_scales=None, gains=None, call: int = 0,
+           span: int = 1, streams: int = 1) -> torch.Tensor:
+    """One whole quantized linear (pre-pass + GEMM) through ``sq_linear``."""
+    _require_cuda(x, "x")
+    x = x.contiguous()
+    k = x.shape[-1]
+    rows = x.numel() // k
+    n = packed.shape[0]
+    lib = _lib.load_library()
+    nbytes = lib.sq_workspace_bytes(rows, k)
+    workspace = torch.empty((max(nbytes, 1),), device=x.device, dtype=torch.uint8)
+    out = torch.empty((*x.shape[:-1], n), device=x.device, dtype=x.dtype)
+    group = w_scales.dtype == torch.float16
+    calls = 0 if act_scales is None else act_scales.numel()
+    with torch.cuda.device(x.device):
+        status = lib.sq_linear(
+            x.data_ptr(), _DTYPES[x.dtype], rows, k, n, int(abits),
+            _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
+            _ptr(inverse), _ptr(signs), int(rht_block), _ptr(act_scales), _ptr(gains), int(calls), int(call),
+            int(span), int(streams), int(x.shape[-2]),
+            packed.data_ptr(), w_scales.data_ptr(), _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32,
+            _ptr(bias), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
+    _lib.check(status, "sq_linear")
+    return out
+
+
+def device_status() -> int:
+    """Read and clear the device-side status word (synchronises)."""
+    return int(_lib.load_library().sq_device_status())

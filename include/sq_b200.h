@@ -1,0 +1,135 @@
+/* C ABI of libsq_b200.so: the SteerQuant quantized-linear path on NVIDIA B200 (sm_100a).
+ *
+ * One quantized linear is two launches on the caller's stream:
+ *   sq_prepass  bf16/fp16 activations -> [randomized Hadamard] -> [1/D] -> int8 codes + fp32 row scales
+ *   sq_gemm     codes x packed-int4 weights -> int32 (tcgen05 kind::i8, TMEM) -> scales, bias -> bf16/fp16
+ *
+ * All pointers are DEVICE pointers unless a name ends in _host.  Nothing here allocates,
+ * synchronises the host or reads device memory on the host, so every call may be recorded into
+ * a CUDA graph.  `stream` is a cudaStream_t passed as void*.  Every function returns 0 on
+ * success, a negative SQ_ERR_* for a rejected argument (nothing was launched) or the positive
+ * CUDA error of a failed launch.  sq_status_string() names any of them.
+ *
+ * Citations name the file and lines of the reference project (CathyyW/Fastwamjoint-quantization,
+ * paths below src/fastwam_steerquant/) whose role each entry point takes over.
+ */
+#ifndef SQ_B200_H
+#define SQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SQ_OK 0
+#define SQ_ERR_NULL (-1)      /* a required pointer is null                            */
+#define SQ_ERR_SHAPE (-2)     /* sizes violate the alignment rules stated per function */
+#define SQ_ERR_ENUM (-3)      /* an enum-like int argument is out of range             */
+#define SQ_ERR_INDEX (-4)     /* schedule index outside [0, calls)                     */
+#define SQ_ERR_DRIVER (-5)    /* the CUDA driver refused a tensor-map encode           */
+#define SQ_ERR_WORKSPACE (-6) /* workspace smaller than sq_workspace_bytes()           */
+#define SQ_ERR_DEVICE_WAIT (-7) /* a kernel gave up a bounded wait (see sq_device_status) */
+
+/* element types of activations / outputs */
+#define SQ_BF16 0
+#define SQ_FP16 1
+
+/* activation quantizer modes */
+#define SQ_ACT_STATIC 0 /* per-call scale, per-stream gain: code = rn(x * inv_d * (gain / scale)) */
+#define SQ_ACT_TOKEN 1  /* per-token dynamic:               code = rn(x * inv_d / (amax / qmax))  */
+
+/* order of the codes along K inside each run of 8 */
+#define SQ_CODES_NATURAL 0 /* k, k+1, ..., k+7                                                     */
+#define SQ_CODES_EVEN_ODD 1 /* k, k+2, k+4, k+6, k+1, k+3, k+5, k+7 (what sq_gemm unpacks fastest) */
+
+/* weight-scale forms */
+#define SQ_WSCALE_CHANNEL_F32 0 /* float  [N]          (reference: checkpoint.py:49-50, runtime.py:89) */
+#define SQ_WSCALE_GROUP_F16 1   /* __half [N, K / 128] (group-128 scheme of the benchmark)             */
+
+/* Fused activation pre-pass.
+ * Replaces the producer kernels quantize_static_per_tensor_stream_kernel (kernels/w4a8/csrc/w4a8.cu:838-881),
+ * quantize_dynamic_per_token_kernel (w4a8.cu:693-747), quantize_static_stream_s4_kernel and
+ * quantize_per_token_s4_kernel (kernels/w4a4/csrc/w4a4.cu:1085-1124, 918-961) and the rotate-then-quantize
+ * producer (kernels/w4a4/csrc/rht.cuh:8-61) for block-local power-of-two rotations.
+ *
+ *   x            [rows, K] bf16 or fp16 (x_dtype), row-major, 16-byte aligned
+ *   abits        8 or 4: codes are clamped to +-127 or +-7 (symmetric, as the reference)
+ *   mode         SQ_ACT_STATIC or SQ_ACT_TOKEN
+ *   inv_d        [K] fp32 multiplier 1/D, or null
+ *   signs        [K] fp32 +-1, or null for no rotation
+ *   rht_block    rotation block length: a power of two in [8, 256] dividing K (ignored when signs is null).
+ *                The rotated value is rounded to x_dtype before quantization (reference contract
+ *                rht_install.py:46-49, rht.cuh:55-56).
+ *   act_scale    static mode: pointer to THIS call's activation scale (one float)
+ *   gains        static mode: pointer to THIS call's row of stream gains [streams]
+ *   span         static mode: > 0: row r belongs to stream (r / span) % streams;
+ *                < 0: rows with (r % seq_tokens) >= seq_tokens + span belong to stream 1, others to 0
+ *                (w4a8.cu:857-861)
+ *   codes_layout SQ_CODES_NATURAL or SQ_CODES_EVEN_ODD
+ *   pack_int4    0: int8 codes [rows, K]; 1: two codes per byte [rows, K/2], low nibble = even k
+ *                (only with abits == 4 and SQ_CODES_NATURAL; the reference's A4 storage, w4a4.cu:1119-1123)
+ *   codes        out, 16-byte aligned
+ *   row_scales   out fp32 [rows]: static: scale / gain; token: max(amax, tiny) / qmax
+ * Alignment: K % 8 == 0 and K <= 32768.
+ */
+int sq_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode,
+               const float* inv_d, const float* signs, int rht_block,
+               const float* act_scale, const float* gains, int64_t span, int64_t streams, int64_t seq_tokens,
+               int codes_layout, int pack_int4, void* codes, float* row_scales, void* stream);
+
+/* Quantized GEMM with fused epilogue.
+ * Replaces PlainFusedEpilogueGemm + launch_packed_w4a8_gemm (w4a8.cu:309-381, 891-922) and
+ * FusedEpilogueGemm + launch_fused_w4a4_gemm (w4a4.cu:257-371, 1217-1249).
+ *
+ *   codes        int8 [M, K] from sq_prepass (codes_layout says in which order)
+ *   w_packed     uint8 [N, K/2]: two's-complement nibbles, low nibble = even k (kernels/w4a8/ops.py:8-14)
+ *   w_scales     float [N] (SQ_WSCALE_CHANNEL_F32) or __half [N, K/128] (SQ_WSCALE_GROUP_F16)
+ *   row_scales   float [M]
+ *   bias         [N] in out_dtype, or null
+ *   out          [M, N] bf16/fp16 (out_dtype), row-major
+ *   acc_dump     null, or int32 [M, N, G] (G = 1 or K/128): the exact integer accumulators, for parity checks
+ * channel form:  out = dtype((float(acc) * row_scale[m]) * w_scale[n] + bias[n])      (w4a8.cu:324-360)
+ * group form:    out = dtype((sum_g float(acc_g) * w_scale[n,g]) * row_scale[m] + bias[n])
+ * Alignment: K % 32 == 0 (K % 128 == 0 in group form), N % 8 == 0, all pointers 16-byte aligned.
+ */
+int sq_gemm(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+            const float* row_scales, const void* bias, void* out, int out_dtype,
+            int64_t M, int64_t N, int64_t K, int32_t* acc_dump, void* stream);
+
+/* Plain-CUDA-core version of sq_gemm with the same arguments and the same results.  It exists so the
+ * tensor-core kernel can be cross-checked on the device; it is not a fallback and nothing dispatches to it. */
+int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+                  const float* row_scales, const void* bias, void* out, int out_dtype,
+                  int64_t M, int64_t N, int64_t K, int32_t* acc_dump, void* stream);
+
+/* Bytes of scratch one linear needs between sq_prepass and sq_gemm (codes + row scales), 256-byte rounded.
+ * Takes the place of the per-call torch::empty of run_static_streams (w4a8.cu:1358-1360). */
+size_t sq_workspace_bytes(int64_t M, int64_t K);
+
+/* One whole linear: sq_prepass into `workspace`, then sq_gemm.  Same role as run_static_streams
+ * (w4a8.cu:1337-1387, w4a4.cu:1517-1574) / symmetric_dynamic (w4a8.cu:1389-1452).
+ * `calls` and `call` select the schedule entry in static mode: act_scales [calls], gains [calls, streams];
+ * an index outside [0, calls) is SQ_ERR_INDEX (w4a8.cu:1587-1628). */
+int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+              const float* inv_d, const float* signs, int rht_block,
+              const float* act_scales, const float* gains, int64_t calls, int64_t call,
+              int64_t span, int64_t streams, int64_t seq_tokens,
+              const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
+              void* out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Reads (and clears) the device-side status word of the current device.  Kernels never spin forever:
+ * a wait that exceeds its time limit records a code here and the kernel returns.  0 = no kernel gave up.
+ * Synchronises the device; not for use during stream capture. */
+int sq_device_status(void);
+
+const char* sq_status_string(int status);
+
+/* Library build tag, e.g. "sq_b200 sm_100a". */
+const char* sq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SQ_B200_H */

@@ -1,0 +1,63 @@
+"""The shared library loads and exports every symbol ``include/sq_b200.h`` declares
+(no compute calls: this runs without a GPU), and host-side argument checks reject
+bad calls before any launch."""
+import ctypes
+import importlib
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def lib(pkg):
+    import __graft_entry__ as entry
+    entry.build()
+    return importlib.import_module("fastwamjoint_quantization_b200._lib")
+
+
+def test_header_symbols_are_exported(lib):
+    header = (ROOT / "include" / "sq_b200.h").read_text()
+    declared = set(re.findall(r"^(?:int|size_t|const char\*)\s+(sq_\w+)\s*\(", header, flags=re.M))
+    assert declared, "no declarations parsed from the header"
+    handle = lib.load_library()
+    for name in declared:
+        assert hasattr(handle, name), f"{name} is declared but not exported"
+    assert declared == set(lib.EXPORTED)
+
+
+def test_status_strings_and_version(lib):
+    handle = lib.load_library()
+    assert handle.sq_version().decode().startswith("sq_b200")
+    assert lib.status_string(0) == "ok"
+    assert "index" in lib.status_string(lib.ERR_INDEX)
+    assert "workspace" in lib.status_string(lib.ERR_WORKSPACE)
+
+
+def test_workspace_bytes(lib):
+    handle = lib.load_library()
+    assert handle.sq_workspace_bytes(0, 1024) == 0
+    assert handle.sq_workspace_bytes(3, 1024) == 3 * 1024 + 256
+    assert handle.sq_workspace_bytes(2048, 3072) == 2048 * 3072 + 2048 * 4
+
+
+def test_argument_errors_need_no_gpu(lib):
+    handle = lib.load_library()
+    fake = ctypes.c_void_p(4096)  # never dereferenced: rejected before any launch
+    # null pointers
+    assert handle.sq_prepass(None, 0, 4, 256, 8, 1, None, None, 0, None, None, 1, 1, 4, 0, 0, fake, fake, None) == lib.ERR_NULL
+    # K not a multiple of 8
+    assert handle.sq_prepass(fake, 0, 4, 250, 8, 1, None, None, 0, None, None, 1, 1, 4, 0, 0, fake, fake, None) == lib.ERR_SHAPE
+    # bad bit width
+    assert handle.sq_prepass(fake, 0, 4, 256, 5, 1, None, None, 0, None, None, 1, 1, 4, 0, 0, fake, fake, None) == lib.ERR_ENUM
+    # rotation block not a power of two
+    assert handle.sq_prepass(fake, 0, 4, 384, 4, 1, None, fake, 96, None, None, 1, 1, 4, 0, 0, fake, fake, None) == lib.ERR_SHAPE
+    # GEMM: group scales need K % 128 == 0; N % 8 != 0; out-of-range schedule index in sq_linear
+    assert handle.sq_gemm(fake, 1, fake, fake, 1, fake, None, fake, 0, 4, 8, 160, None, None) == lib.ERR_SHAPE
+    assert handle.sq_gemm(fake, 1, fake, fake, 0, fake, None, fake, 0, 4, 7, 256, None, None) == lib.ERR_SHAPE
+    assert handle.sq_linear(fake, 0, 4, 256, 8, 4, 0, fake, None, 0, fake, fake, 10, 10, 2, 2, 4,
+                            fake, fake, 0, None, fake, fake, 1 << 20, None) == lib.ERR_INDEX
+    assert handle.sq_linear(fake, 0, 4, 256, 8, 4, 0, fake, None, 0, fake, fake, 10, 0, 2, 2, 4,
+                            fake, fake, 0, None, fake, fake, 16, None) == lib.ERR_WORKSPACE

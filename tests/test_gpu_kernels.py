@@ -1,0 +1,204 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI.
+
+Bars: activation codes and int32 accumulators bit-exact; post-rotation codes may differ
+by at most 1 on at most 0.1 % of elements; outputs within 1e-2 relative Frobenius error
+(the cross-check kernel, which keeps the oracle's fp32 operation order, must be bit-exact).
+"""
+import importlib
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native(pkg):
+    return importlib.import_module("fastwamjoint_quantization_b200.native")
+
+
+@pytest.fixture(autouse=True)
+def no_device_timeouts(native):
+    yield
+    torch.cuda.synchronize()
+    assert native.device_status() == 0, "a kernel gave up a bounded wait"
+
+
+def even_odd(codes: torch.Tensor) -> torch.Tensor:
+    """natural -> even-k-first order inside each run of 8"""
+    m, k = codes.shape
+    runs = codes.reshape(m, k // 8, 8)
+    return torch.cat((runs[..., 0::2], runs[..., 1::2]), dim=-1).reshape(m, k)
+
+
+def rel_fro(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+
+def assert_codes(got, want, rotated):
+    if not rotated:
+        assert torch.equal(got, want)
+        return
+    diff = (got.int() - want.int()).abs()
+    assert diff.max() <= 1
+    assert (diff != 0).float().mean().item() <= 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k", [(1, 128), (33, 1024), (50, 3072), (7, 12288), (5, 14336), (3, 96)])
+@pytest.mark.parametrize("abits,rotate", [(8, False), (4, False), (4, True), (8, True)])
+def test_prepass_token(native, oracle, dtype, m, k, abits, rotate):
+    if rotate and k % 128:
+        pytest.skip("rotation block must divide K")
+    gen = torch.Generator().manual_seed(m * 131 + k)
+    x = torch.randn(m, k, generator=gen)
+    x[:, torch.randperm(k, generator=gen)[: max(1, k // 100)]] *= 20
+    if m > 2:
+        x[1] = 0  # all-zero token: scale clamps at 1e-8, codes are 0
+    x = x.to(dtype)
+    signs = oracle.rht_signs(k, seed=0, module_name="linear") if rotate else None
+    inverse = torch.rand(k, generator=gen) + 0.5 if (m % 2) else None
+    want_codes, want_scales = oracle.token_codes(x, bits=abits, signs=signs, inverse=inverse)
+    dev = lambda t: None if t is None else t.cuda()
+    codes, scales = native.prepass(x.cuda(), abits=abits, mode="token", signs=dev(signs), inverse=dev(inverse),
+                                   codes_layout=0)
+    assert_codes(codes.cpu(), want_codes, rotate)
+    assert torch.equal(scales.cpu(), want_scales)
+    codes_eo, _ = native.prepass(x.cuda(), abits=abits, mode="token", signs=dev(signs), inverse=dev(inverse),
+                                 codes_layout=1)
+    assert torch.equal(codes_eo.cpu(), even_odd(codes.cpu()))
+    if abits == 4:
+        packed, _ = native.prepass(x.cuda(), abits=4, mode="token", signs=dev(signs), inverse=dev(inverse),
+                                   codes_layout=0, pack_int4=True)
+        assert torch.equal(packed.cpu(), oracle.pack_signed_int4(codes.cpu()))
+
+
+@pytest.mark.parametrize("block", [8, 16, 32, 64, 128, 256])
+def test_prepass_rotation_blocks(native, oracle, block):
+    gen = torch.Generator().manual_seed(block)
+    x = (torch.randn(9, 1024, generator=gen) * 2).bfloat16()
+    signs = oracle.rht_signs(1024, seed=3, module_name="blocks")
+    want, scales = oracle.token_codes(x, bits=8, signs=signs, block=block)
+    codes, got_scales = native.prepass(x.cuda(), abits=8, mode="token", signs=signs.cuda(), rht_block=block,
+                                       codes_layout=0)
+    assert_codes(codes.cpu(), want, True)
+    assert torch.allclose(got_scales.cpu(), scales, rtol=1e-6, atol=0)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k,counts,batch", [(32, 1024, (16, 16), 1), (294, 3072, (98, 98, 98), 1),
+                                              (129, 1024, (128, 1), 2)])
+@pytest.mark.parametrize("abits", [8, 4])
+def test_prepass_static_schedule(native, oracle, dtype, m, k, counts, batch, abits):
+    """Shapes, layouts and schedule of the reference's own tests (tests/test_wam_w4a4.py:17-36)."""
+    gen = torch.Generator().manual_seed(m + k)
+    x = (torch.randn(batch, m, k, generator=gen) * 0.5).to(dtype)
+    inverse = torch.pow(2.0, torch.randint(-1, 2, (k,), generator=gen).float())
+    gains = torch.ones(10, len(counts))
+    gains[0] = torch.tensor([0.5, 2.0, 1.0][: len(counts)])
+    gains[9] = torch.tensor([2.0, 0.5, 1.0][: len(counts)])
+    scales = torch.linspace(0.125, 0.25, 10) if abits == 4 else torch.linspace(0.01, 0.03, 10)
+    span = counts[0] if len(set(counts)) == 1 else -counts[1]
+    for call in (0, 9):
+        want, want_rows = oracle.static_codes(x, bits=abits, inverse=inverse, activation_scales=scales, gains=gains,
+                                              token_counts=counts, call=call)
+        codes, rows = native.prepass(x.cuda(), abits=abits, mode="static", inverse=inverse.cuda(),
+                                     act_scale=scales.cuda()[call:], gains=gains.cuda()[call], span=span,
+                                     streams=len(counts), codes_layout=0)
+        assert torch.equal(codes.cpu().reshape(batch, m, k), want)
+        assert torch.equal(rows.cpu(), want_rows.repeat(batch))
+
+
+GEMM_SHAPES = [(256, 1024, 1024), (96, 512, 256), (1, 128, 8), (300, 3072, 384), (17, 256, 136), (520, 1024, 128)]
+
+
+@pytest.mark.parametrize("m,k,n", GEMM_SHAPES)
+@pytest.mark.parametrize("abits", [8, 4])
+def test_gemm_group_scheme(native, oracle, m, k, n, abits):
+    case = oracle.prepare_token_linear(m, k, n, abits=abits, seed=0)
+    want = oracle.linear_token(case["x"], case["qweight"], case["weight_scales"], case["bias"], abits=abits,
+                               signs=case["signs"])
+    packed = oracle.pack_signed_int4(case["qweight"]).cuda()
+    wscales = case["weight_scales"].cuda()
+    bias = (torch.randn(n, generator=torch.Generator().manual_seed(n)) * 0.01).bfloat16()
+    want_out = oracle.epilogue_group(want["acc"], case["weight_scales"], want["row_scales"], bias, torch.bfloat16)
+    codes_nat = want["codes"].cuda()
+    row_scales = want["row_scales"].cuda()
+    for layout, codes in ((0, codes_nat), (1, even_odd(want["codes"]).cuda())):
+        ref_out, ref_acc = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
+                                       codes_layout=layout, want_accumulators=True, check_kernel=True)
+        assert torch.equal(ref_acc.cpu().long(), want["acc"])
+        assert torch.equal(ref_out.cpu().view(torch.int16), want_out.view(torch.int16))
+        out, acc = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
+                               codes_layout=layout, want_accumulators=True)
+        assert torch.equal(acc.cpu().long(), want["acc"])
+        assert rel_fro(out.cpu(), want_out) < 1e-2
+        # same numbers up to the fused multiply-add in the drain: within one bf16 step almost everywhere
+        assert rel_fro(out.cpu(), want_out) < 2e-3
+        plain = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
+                            codes_layout=layout)
+        assert torch.equal(plain, out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,k,n", [(32, 1024, 3072), (32, 3072, 1024), (129, 1024, 3072), (294, 3072, 3072),
+                                   (294, 3072, 14336), (294, 14336, 3072)])
+def test_gemm_channel_scheme_exact(native, oracle, dtype, m, k, n):
+    """The reference's exact W4A4 test (tests/test_wam_w4a4.py:39-58): per-channel scales,
+    static schedule, atol = rtol = 0 against the kernel-order oracle."""
+    gen = torch.Generator().manual_seed(m + k + n)
+    batch = 2 if m == 129 else 1
+    x = (torch.randn(batch, m, k, generator=gen) * 0.5).to(dtype)
+    qw = torch.randint(-7, 8, (n, k), generator=gen, dtype=torch.int8)
+    ws = torch.full((n,), 1 / 512)
+    inverse = torch.pow(2.0, torch.randint(-1, 2, (k,), generator=gen).float())
+    bias = (torch.randn(n, generator=gen) * 0.01).to(dtype)
+    counts = (16, 16) if m == 32 else (128, 1) if m == 129 else (98, 98, 98)
+    gains = torch.ones(10, len(counts))
+    gains[0] = torch.tensor([0.5, 2.0, 1.0][: len(counts)])
+    gains[9] = torch.tensor([2.0, 0.5, 1.0][: len(counts)])
+    scales = torch.linspace(0.125, 0.25, 10)
+    packed = oracle.pack_signed_int4(qw).cuda()
+    span = counts[0] if len(set(counts)) == 1 else -counts[1]
+    for call in (0, 9):
+        want = oracle.linear_static(x, qw, ws, bias, inverse, scales, gains, counts, call, abits=4)
+        out = native.linear(x.cuda(), packed, ws.cuda(), bias.cuda(), abits=4, mode="static", inverse=inverse.cuda(),
+                            act_scales=scales.cuda(), gains=gains.cuda(), call=call, span=span, streams=len(counts))
+        assert out.shape == (batch, m, n) and out.dtype == dtype
+        torch.testing.assert_close(out.cpu(), want["out"], rtol=0, atol=0)
+        codes, rows = native.prepass(x.cuda(), abits=4, mode="static", inverse=inverse.cuda(),
+                                     act_scale=scales.cuda()[call:], gains=gains.cuda()[call], span=span,
+                                     streams=len(counts))
+        _, acc = native.gemm(codes, packed, ws.cuda(), rows, bias.cuda(), out_dtype=dtype, want_accumulators=True)
+        assert torch.equal(acc.cpu().long()[..., 0], want["acc"])
+
+
+def test_linear_graph_capture_and_replay_after_mutation(native, oracle):
+    """Capture in a CUDA graph, change the input in place, replay: equals a fresh eager run bit for bit
+    (tests/test_w4a8.py:32-37)."""
+    case = oracle.prepare_token_linear(294, 3072, 3072, abits=8, seed=1)
+    x = case["x"].cuda()
+    packed = oracle.pack_signed_int4(case["qweight"]).cuda()
+    ws = case["weight_scales"].cuda()
+    run = lambda: native.linear(x, packed, ws, None, abits=8, mode="token")
+    eager = run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = run()
+    graph.replay()
+    assert torch.equal(captured, eager)
+    x.mul_(0.7)
+    graph.replay()
+    assert torch.equal(captured, run())
+
+
+def test_rejected_calls_raise(native, oracle):
+    case = oracle.prepare_token_linear(8, 256, 16, abits=8, seed=0)
+    packed = oracle.pack_signed_int4(case["qweight"]).cuda()
+    with pytest.raises(RuntimeError, match="index"):
+        native.linear(case["x"].cuda(), packed, torch.ones(16).cuda(), None, abits=8, mode="static",
+                      inverse=torch.ones(256).cuda(), act_scales=torch.ones(2).cuda(), gains=torch.ones(2, 2).cuda(),
+                      call=2, span=4, streams=2)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        native.prepass(case["x"], abits=8, mode="token")
