@@ -201,14 +201,42 @@ def main():
         wss.append(case["weight_scales"].to(device).clone())
     bias = case["bias"].to(device)
 
+    lib_ws = native._lib.load_library().sq_workspace_bytes(m, k)
+    outs = [torch.empty((m, n), device=device, dtype=torch.bfloat16) for _ in range(nsets)]
+    workspace = torch.empty((lib_ws,), device=device, dtype=torch.uint8)
+
     def step(i):
         j = i % nsets
-        return native.linear(xs[j], packs[j], wss[j], bias, abits=abits, mode="token", signs=signs)
+        return native.linear(xs[j], packs[j], wss[j], bias, abits=abits, mode="token", signs=signs, out=outs[j],
+                             workspace=workspace)
 
     def barrier():
         if distributed:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def graph_of(fn, count):
+        """Capture `count` calls of fn(i) into one CUDA graph (launch cost leaves the timed region, as in
+        the deployed path, where a whole denoising step is one graph)."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn(0)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(count):
+                fn(i)
+        return graph
+
+    def timed_replay(graph):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
 
     # correctness of what is being timed (small slice, against the oracle)
     out0 = step(0)
@@ -219,39 +247,38 @@ def main():
     if not err < 1e-2:
         raise SystemExit(f"bench output differs from the oracle: relative Frobenius error {err}")
 
-    for i in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
         step(i)
+    step_graph = graph_of(step, args.steps)
+    step_graph.replay()  # one untimed replay of the whole graph
     sampler = ClockSampler(local_rank)
     sampler.start()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        step(i)
+    step_graph.replay()  # exactly args.steps steps
     e1.record()
     barrier()
     elapsed_ms = e0.elapsed_time(e1)
 
-    # dominant kernel alone (the GEMM), same rotation, for the roofline
+    # the two kernels alone, same rotation of inputs, for the roofline
     pre = [native.prepass(xs[j], abits=abits, mode="token", signs=signs) for j in range(nsets)]
-    for i in range(3):
-        native.gemm(pre[i % nsets][0], packs[i % nsets], wss[i % nsets], pre[i % nsets][1], bias, out_dtype=torch.bfloat16)
-    torch.cuda.synchronize()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g0.record()
-    for i in range(args.steps):
+
+    def gemm_only(i):
         j = i % nsets
-        native.gemm(pre[j][0], packs[j], wss[j], pre[j][1], bias, out_dtype=torch.bfloat16)
-    g1.record()
-    torch.cuda.synchronize()
-    gemm_ms = g0.elapsed_time(g1) / args.steps
-    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    p0.record()
-    for i in range(args.steps):
-        native.prepass(xs[i % nsets], abits=abits, mode="token", signs=signs)
-    p1.record()
-    torch.cuda.synchronize()
-    prepass_ms = p0.elapsed_time(p1) / args.steps
+        native.gemm(pre[j][0], packs[j], wss[j], pre[j][1], bias, out_dtype=torch.bfloat16, out=outs[j])
+
+    def prepass_only(i):
+        j = i % nsets
+        native.prepass(xs[j], abits=abits, mode="token", signs=signs, out=pre[j])
+
+    gemm_graph = graph_of(gemm_only, args.steps)
+    timed_replay(gemm_graph)
+    gemm_ms = timed_replay(gemm_graph) / args.steps
+    prepass_graph = graph_of(prepass_only, args.steps)
+    timed_replay(prepass_graph)
+    prepass_ms = timed_replay(prepass_graph) / args.steps
 
     # end to end through the public call with HOST buffers: pinned x -> device, linear, result -> pinned host
     x_host = case["x"].pin_memory()
@@ -314,13 +341,14 @@ def main():
         roofline["prepass_gbs"] = (2 * m * k + m * k + 4 * m) / (prepass_ms * 1e-3) / 1e9
         line = {
             "metric": "W4A%d%s GEMM int-TOPS" % (abits, "+RHT" if rotate else ""), "value": tops, "unit": "TOPS",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8 x int4 -> int32", "data": "synthetic",
             "config": {"workload": args.workload, "M_per_gpu": m, "K": k, "N": n, "abits": abits, "rht": rotate,
                        "weight_scales": "fp16 group-128", "activation_scales": "per-token",
                        "sharding": "tokens (M) across ranks, weights replicated, no collective",
-                       "l2": "rotating %d input sets (%.0f MB > 126 MB L2)" % (nsets, nsets * set_bytes / 1e6)},
+                       "l2": "rotating %d input sets (%.0f MB > 126 MB L2)" % (nsets, nsets * set_bytes / 1e6),
+                       "launch": "the K steps are replayed as one CUDA graph"},
             "gpu_launches": 2 * args.steps,
             "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms / e2e_steps},

@@ -26,6 +26,8 @@ _SIGNATURES = {
                         c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "sq_gemm_check": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                               c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "sq_gemm_timeline": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                 c_void_p, c_void_p]),
     "sq_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "sq_linear": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,

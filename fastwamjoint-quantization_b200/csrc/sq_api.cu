@@ -169,6 +169,13 @@ int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, con
                                static_cast<cudaStream_t>(stream));
 }
 
+int sq_gemm_timeline(const void* codes, const void* w_packed, const void* w_scales, const float* row_scales,
+                     const void* bias, void* out, int64_t M, int64_t N, int64_t K, long long* timeline, void* stream) {
+  return sq::launch_gemm_timeline(make_args(codes, SQ_CODES_EVEN_ODD, w_packed, w_scales, SQ_WSCALE_GROUP_F16, row_scales,
+                                            bias, out, SQ_BF16, M, N, K, nullptr),
+                                  timeline, static_cast<cudaStream_t>(stream));
+}
+
 size_t sq_workspace_bytes(int64_t M, int64_t K) {
   if (M < 0 || K < 0) return 0;
   return sq::round256(static_cast<size_t>(M) * static_cast<size_t>(K)) + sq::round256(static_cast<size_t>(M) * 4u);

@@ -1,7 +1,7 @@
 // W4A8 / W4A4 GEMM on the 5th-generation tensor cores: out[m, n] = sum_k a[m, k] * w[n, k].
 //
 // The MMA runs "weights as rows": the UMMA M dimension (TMEM lanes) is 128 output channels,
-// the UMMA N dimension (TMEM columns) is up to 256 tokens.  A TMEM lane therefore belongs to ONE
+// the UMMA N dimension (TMEM columns) is up to 160 tokens.  A TMEM lane therefore belongs to ONE
 // output channel, so the per-group weight scale is a per-thread scalar when the accumulator is
 // drained, and small token counts map to a small UMMA N instead of a wasted 128-row tile.
 //
@@ -44,12 +44,17 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr uint32_t kMagicBits = 0x4B400000u;               // float 12582912 = 1.5 * 2^23
 constexpr float kMagicFloat = 12582912.0f;
 
+// Timeline capture (debug entry point sq_gemm_timeline): CTA 0 stamps clock64() per K block.
+constexpr int kTraceSlots = 512;
+enum TraceRole { kTrTmaIssue = 0, kTrConvStart, kTrConvDone, kTrMmaAccFree, kTrMmaIssue, kTrDrainStart,
+                 kTrDrainRelease, kTrDrainDone, kTraceRoles };
+
 constexpr int kNumConverterWarps = 4;
 constexpr int kNumDrainWarps = 8;
 
 __host__ __device__ constexpr int stages_for(int tok) {
   // shared memory per stage: unpacked weights + codes + packed weights
-  return tok == 256 ? 4 : tok == 128 ? 5 : tok == 64 ? 7 : 8;
+  return tok == 160 ? 5 : tok == 128 ? 5 : tok == 64 ? 7 : 8;
 }
 __host__ __device__ constexpr uint32_t stage_bytes(int tok) { return kWBytes + tok * kBlockK + kPackedBytes; }
 __host__ __device__ constexpr uint32_t smem_bytes_for(int tok) {
@@ -62,9 +67,12 @@ struct TcParams {
   const void* bias;
   void* out;
   int32_t* acc_dump;
+  long long* timeline;  // kTrace only: [kTraceRoles][kTraceSlots] SM clock stamps written by CTA 0
   int* status;
   int64_t M, N, K;
   int ch_tiles, tok_tiles, k_blocks;
+  int tok_tile;   // tokens per tile at run time: a multiple of 16, <= TOK
+  int half_cols;  // columns drained by the first warp of each lane quarter (the second takes the rest)
   int out_dtype;
 };
 
@@ -86,29 +94,59 @@ __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.al
 template <int kRegs>
 __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs)); }
 
+// Two fp32 values in one 64-bit register, for the packed add / fma of sm_100.
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  uint32_t a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+  lo = __uint_as_float(a);
+  hi = __uint_as_float(b);
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code) {
   *abort_flag = 1;
   atomicCAS(status, 0, code);
 }
 
-// TOK    tokens per tile (TMEM columns per accumulator, rows of the codes box)
+// TOK    capacity in tokens of one tile (TMEM columns per accumulator, rows of a codes stage); the
+//        tile actually used, p.tok_tile <= TOK, is chosen per call so the tiles fill the SMs evenly
 // kGroup one accumulator per 128-K weight group (fp16 scales [N, K/128]); otherwise one per tile (fp32 [N])
 // kMagic group mode only: TMEM accumulators start at the bit pattern of 1.5 * 2^23, so the drained word
 //        re-read as a float is 12582912 + acc exactly and the int->float conversion is one subtraction
 // kEvenOdd codes are stored even-k-first inside each run of 8 (no byte interleave needed when unpacking)
 // kDump  also write the exact integer accumulators
-template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT>
+template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TcParams p) {
   static_assert(!kMagic || kGroup, "the magic-number drain needs |16 acc| < 2^22, true only per 128-K group");
   constexpr int S = stages_for(TOK);
   constexpr uint32_t kXBytes = TOK * kBlockK;
-  constexpr int kColsPerHalf = TOK / 2;           // columns drained by one warp of a lane quarter
-  constexpr int kChunk = 16;                      // columns per tcgen05.ld
-  constexpr int kChunks = kColsPerHalf / kChunk;  // per drain thread
-  constexpr uint32_t kTmemCols = 2 * TOK < 32 ? 32 : 2 * TOK;
-  static_assert(kColsPerHalf % kChunk == 0, "tile too narrow");
+  // Each of the two drain warps of a lane quarter owns up to kColsPerHalf token columns and reads them
+  // with loads that are all in flight at once (kFull 32-column loads plus one 16-column load when
+  // kTail): a tcgen05.ld round trip costs a few hundred cycles, so the loads of one accumulator must
+  // overlap each other, not follow each other.  80 columns + 80 fp32 sums per thread is what fits the
+  // register file next to the other roles, hence 160 tokens per tile at most.
+  constexpr int kColsPerHalf = TOK == 160 ? 80 : TOK == 128 ? 64 : TOK == 64 ? 32 : 16;
+  constexpr int kFull = kColsPerHalf / 32;
+  constexpr bool kTail = (kColsPerHalf % 32) != 0;
+  constexpr uint32_t kBufStride = TOK > 128 ? 256 : TOK > 64 ? 128 : TOK;  // TMEM columns between accumulators
+  constexpr uint32_t kTmemCols = 2 * kBufStride < 32 ? 32 : 2 * kBufStride;
+  static_assert(TOK == 160 || TOK == 128 || TOK == 64 || TOK == 32, "tile capacities");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -155,19 +193,23 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   const int num_tiles = p.ch_tiles * p.tok_tiles;
+  const bool tracing = kTrace && blockIdx.x == 0 && p.timeline != nullptr;
+  auto stamp = [&](int role, uint32_t slot) {
+    if (kTrace && tracing && slot < kTraceSlots) p.timeline[role * kTraceSlots + slot] = clock64();
+  };
   const int groups = kGroup ? p.k_blocks : 1;
   const int blocks_per_group = kGroup ? 1 : p.k_blocks;
 
   if (warp < 4) {
     // ------------------------------------------------------------------ control warpgroup
-    reg_dec<56>();
+    reg_dec<32>();
     if (warp == 0 && lane == 0) {
       // TMA producer
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int ch0 = (tile % p.ch_tiles) * kBlockCh;
-        const int tok0 = (tile / p.ch_tiles) * TOK;
+        const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t s = it % S, phase = (it / S) & 1u;
           if (!mbar_wait_bounded(bar_empty + 8 * s, phase ^ 1u, abort_flag, kWaitLimitNs)) {
@@ -175,7 +217,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_full + 8 * s, kXBytes + kPackedBytes);
+          stamp(kTrTmaIssue, it);
+          mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(p.tok_tile) * kBlockK + kPackedBytes);
           tma_load_2d(p_ring + s * kPackedBytes, &tmap_packed, kb * (kBlockK / 2), ch0, bar_full + 8 * s);
           tma_load_2d(x_ring + s * kXBytes, &tmap_codes, kb * kBlockK, tok0, bar_full + 8 * s);
         }
@@ -185,9 +228,9 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       uint32_t it = 0, git = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tok0 = (tile / p.ch_tiles) * TOK;
+        const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
         const int64_t left = p.M - tok0;
-        const int tok_count = left < TOK ? static_cast<int>(left) : TOK;
+        const int tok_count = left < p.tok_tile ? static_cast<int>(left) : p.tok_tile;
         const uint32_t umma_n = static_cast<uint32_t>((tok_count + 15) & ~15);
         const uint32_t idesc = umma_idesc_i8(kBlockCh, umma_n);
         for (int g = 0; g < groups && ok; ++g, ++git) {
@@ -198,7 +241,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             break;
           }
           tc_fence_after_sync();
-          const uint32_t tmem_d = tmem_base + buf * TOK;
+          stamp(kTrMmaAccFree, git);
+          const uint32_t tmem_d = tmem_base + buf * kBufStride;
           for (int kb = 0; kb < blocks_per_group; ++kb, ++it) {
             const uint32_t s = it % S, phase = (it / S) & 1u;
             if (!mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs) ||
@@ -208,6 +252,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               break;
             }
             tc_fence_after_sync();
+            stamp(kTrMmaIssue, it);
             const uint64_t desc_a = umma_desc_k128(w_ring + s * kWBytes);
             const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
 #pragma unroll
@@ -224,7 +269,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ converter warpgroup
-    reg_dec<88>();
+    reg_dec<56>();
     const int ctid = threadIdx.x - 128;  // 0..127
     uint32_t it = 0;
     bool ok = true;
@@ -236,6 +281,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           ok = false;
           break;
         }
+        if (ctid == 0) stamp(kTrConvStart, it);
         const uint32_t src = p_ring + s * kPackedBytes;
         const uint32_t dst = w_ring + s * kWBytes;
 #pragma unroll
@@ -270,96 +316,131 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_wfull + 8 * s);
+        if (ctid == 0) stamp(kTrConvDone, it);
       }
     }
   } else {
     // ------------------------------------------------------------------ drain warpgroups
-    reg_inc<184>();
+    reg_inc<208>();
     const int dwarp = warp - 8;           // 0..7
     const int quarter = warp & 3;         // TMEM lane quarter this warp may address
-    const int half = dwarp >> 2;          // which half of the token columns
+    const int half = dwarp >> 2;          // which share of the token columns (two warps per lane quarter)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int ch_in_tile = quarter * 32 + lane;
 
     // hand both accumulators to the MMA warp (after writing the magic start value, if used)
+    const int my_col0 = half * p.half_cols;  // first token column of this warp inside a tile
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
       if (kMagic) {
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c)
-          tmem_st_32x32b_x16_fill(tmem_base + lane_addr + b * TOK + half * kColsPerHalf + c * kChunk, kMagicBits);
+        for (int c = 0; c < kFull; ++c)
+          tmem_st_fill<32>(tmem_base + lane_addr + b * kBufStride + my_col0 + c * 32, kMagicBits);
+        if (kTail) tmem_st_fill<16>(tmem_base + lane_addr + b * kBufStride + my_col0 + kFull * 32, kMagicBits);
         tmem_wait_st();
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);
     }
+    const uint64_t neg_magic2 = pack2(__float_as_uint(-kMagicFloat), __float_as_uint(-kMagicFloat));
+    const __half* scale_row = static_cast<const __half*>(p.w_scales);
 
     uint32_t git = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int ch0 = (tile % p.ch_tiles) * kBlockCh;
-      const int tok0 = (tile / p.ch_tiles) * TOK;
+      const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
       const int64_t left = p.M - tok0;
-      const int tok_count = left < TOK ? static_cast<int>(left) : TOK;
-      const int my_cols = min(max(tok_count - half * kColsPerHalf, 0), kColsPerHalf);  // real tokens in my half
+      const int tok_count = left < p.tok_tile ? static_cast<int>(left) : p.tok_tile;
+      const int my_limit = half == 0 ? p.half_cols : p.tok_tile - p.half_cols;
+      const int my_cols = min(max(tok_count - my_col0, 0), my_limit);  // real tokens in my share
+      const bool tail_on = kTail && my_cols > kFull * 32;  // warp-uniform
       const int64_t n = ch0 + ch_in_tile;
       const bool n_ok = n < p.N;
 
-      float sums[kChunks * kChunk];
+      uint64_t sums[kColsPerHalf / 2];  // fp32 pairs: columns (2j, 2j+1)
 #pragma unroll
-      for (int i = 0; i < kChunks * kChunk; ++i) sums[i] = 0.0f;
+      for (int i = 0; i < kColsPerHalf / 2; ++i) sums[i] = 0ull;
 
-      float scale_next = 0.0f;
-      if (kGroup) {
-        if (n_ok) scale_next = __half2float(__ldg(static_cast<const __half*>(p.w_scales) + n * groups)) * 0.0625f;
-      } else {
-        scale_next = 0.0625f;
+      // group scales are fetched two groups ahead as raw fp16 bits and converted when used, so the
+      // global-load latency never sits in front of a drain
+      unsigned short raw0 = 0, raw1 = 0;
+      if (kGroup && n_ok) {
+        raw0 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups);
+        if (groups > 1) raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + 1);
       }
 
       for (int g = 0; g < groups && ok; ++g, ++git) {
         const uint32_t buf = git & 1u, aphase = (git >> 1) & 1u;
-        const float scale = scale_next;
-        if (kGroup && g + 1 < groups && n_ok)
-          scale_next = __half2float(__ldg(static_cast<const __half*>(p.w_scales) + n * groups + g + 1)) * 0.0625f;
+        float scale = 0.0625f;  // the unpacked weights are 16 x the int4 value
+        if (kGroup) {
+          scale = __half2float(__ushort_as_half(raw0)) * 0.0625f;
+          raw0 = raw1;
+          if (g + 2 < groups && n_ok)
+            raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + g + 2);
+        }
+        const uint64_t scale2 = pack2(__float_as_uint(scale), __float_as_uint(scale));
         if (!mbar_wait_bounded(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9005);
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + lane_addr + buf * TOK + half * kColsPerHalf;
+        if (threadIdx.x == 256) stamp(kTrDrainStart, git);
+        const uint32_t taddr = tmem_base + lane_addr + buf * kBufStride + my_col0;
+        uint32_t r[kFull > 0 ? kFull : 1][32];
+        uint32_t rt[16];
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          if (c * kChunk < my_cols) {  // warp-uniform
-            uint32_t r[kChunk];
-            tmem_ld_32x32b_x16(taddr + c * kChunk, r);
-            tmem_wait_ld();
+        for (int c = 0; c < kFull; ++c)
+          if (c * 32 < my_cols) tmem_ld_chunk(taddr + c * 32, r[c]);
+        if (tail_on) tmem_ld_chunk(taddr + kFull * 32, rt);
+        if (my_cols > 0) tmem_wait_ld();
+        if (kMagic) {
 #pragma unroll
-            for (int i = 0; i < kChunk; ++i) {
-              float value;
+          for (int c = 0; c < kFull; ++c)
+            if (c * 32 < my_cols) tmem_st_fill<32>(taddr + c * 32, kMagicBits);
+          if (tail_on) tmem_st_fill<16>(taddr + kFull * 32, kMagicBits);
+          if (my_cols > 0) tmem_wait_st();
+        }
+        // the accumulator is in registers (and re-armed): give it back before doing the arithmetic
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+        if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
+        auto accumulate = [&](const uint32_t* regs, int width, int col0) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (i < width / 2) {
+              uint64_t value2;
               if (kMagic) {
-                value = __uint_as_float(r[i]) - kMagicFloat;
+                value2 = add2(pack2(regs[2 * i], regs[2 * i + 1]), neg_magic2);
               } else {
-                value = static_cast<float>(static_cast<int32_t>(r[i]));
+                value2 = pack2(__float_as_uint(static_cast<float>(static_cast<int32_t>(regs[2 * i]))),
+                               __float_as_uint(static_cast<float>(static_cast<int32_t>(regs[2 * i + 1]))));
               }
-              sums[c * kChunk + i] = fmaf(value, scale, sums[c * kChunk + i]);
-              if (kDump) {
-                const int col = c * kChunk + i;
+              sums[col0 / 2 + i] = fma2(value2, scale2, sums[col0 / 2 + i]);
+            }
+          }
+          if (kDump) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i < width) {
+                const int col = col0 + i;
                 if (n_ok && col < my_cols) {
-                  const int64_t m = tok0 + half * kColsPerHalf + col;
-                  const int32_t acc16 = kMagic ? static_cast<int32_t>(r[i] - kMagicBits) : static_cast<int32_t>(r[i]);
+                  const int64_t m = tok0 + my_col0 + col;
+                  const int32_t acc16 = kMagic ? static_cast<int32_t>(regs[i] - kMagicBits) : static_cast<int32_t>(regs[i]);
                   p.acc_dump[(m * p.N + n) * groups + g] = acc16 >> 4;
                 }
               }
             }
-            if (kMagic) tmem_st_32x32b_x16_fill(taddr + c * kChunk, kMagicBits);
           }
-        }
-        if (kMagic) tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+        };
+#pragma unroll
+        for (int c = 0; c < kFull; ++c)
+          if (c * 32 < my_cols) accumulate(r[c], 32, c * 32);
+        if (tail_on) accumulate(rt, 16, kFull * 32);
+        if (threadIdx.x == 256) stamp(kTrDrainDone, git);
       }
       if (!ok) break;
 
@@ -369,20 +450,32 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (!kGroup) wscale = __ldg(static_cast<const float*>(p.w_scales) + n);
         const bool has_bias = p.bias != nullptr;
         const float bias = has_bias ? to_float<OutT>(__ldg(static_cast<const OutT*>(p.bias) + n)) : 0.0f;
-        OutT* out = static_cast<OutT*>(p.out);
+        OutT* out = static_cast<OutT*>(p.out) + n;
+        const float* rs_ptr = p.row_scales + tok0 + my_col0;
+        const int64_t m0 = tok0 + my_col0;
 #pragma unroll
-        for (int i = 0; i < kChunks * kChunk; ++i) {
-          if (i < my_cols) {
-            const int64_t m = tok0 + half * kColsPerHalf + i;
-            const float rs = __ldg(p.row_scales + m);
-            float y;
-            if (kGroup) {
-              y = __fmul_rn(sums[i], rs);
+        for (int j = 0; j < kColsPerHalf / 4; ++j) {
+          if (4 * j < my_cols) {
+            float rs[4];
+            if (4 * j + 4 <= my_cols) {
+              const float4 v = __ldg(reinterpret_cast<const float4*>(rs_ptr) + j);
+              rs[0] = v.x; rs[1] = v.y; rs[2] = v.z; rs[3] = v.w;
             } else {
-              y = __fmul_rn(__fmul_rn(sums[i], rs), wscale);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) rs[e] = (4 * j + e < my_cols) ? __ldg(rs_ptr + 4 * j + e) : 0.0f;
             }
-            if (has_bias) y = __fadd_rn(y, bias);
-            out[m * p.N + n] = from_float<OutT>(y);
+            float acc[4];
+            unpack2(sums[2 * j], acc[0], acc[1]);
+            unpack2(sums[2 * j + 1], acc[2], acc[3]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (4 * j + e < my_cols) {
+                float y = __fmul_rn(acc[e], rs[e]);
+                if (!kGroup) y = __fmul_rn(y, wscale);
+                if (has_bias) y = __fadd_rn(y, bias);
+                out[(m0 + 4 * j + e) * p.N] = from_float<OutT>(y);
+              }
+            }
           }
         }
       }
@@ -440,9 +533,28 @@ int sm_count() {
   return cached[dev] > 0 ? cached[dev] : 148;
 }
 
-template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT>
-int launch_variant(const GemmArgs& a, cudaStream_t stream) {
-  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kMagic, kEvenOdd, kDump, OutT>;
+// Tokens per tile: a multiple of 16 up to 160 (two drain warps x 80 columns held in registers at once).  A tile costs about max(t, 96) + 8 "column units" (below
+// ~96 tokens the int4 unpack, not the MMA, sets the pace); the kernel runs ceil(tiles / SMs) waves.
+int pick_tok_tile(int64_t M, int ch_tiles, int sms) {
+  if (M <= 16) return 16;
+  int best = 16;
+  double best_cost = 1e30;
+  for (int t = 16; t <= 160; t += 16) {
+    const int64_t tiles = static_cast<int64_t>(ch_tiles) * ((M + t - 1) / t);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * ((t > 96 ? t : 96) + 8);
+    if (cost <= best_cost) {  // ties go to the wider tile
+      best_cost = cost;
+      best = t;
+    }
+    if (t >= M) break;
+  }
+  return best;
+}
+
+template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
+int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long long* timeline = nullptr) {
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kMagic, kEvenOdd, kDump, OutT, kTrace>;
   constexpr uint32_t smem = smem_bytes_for(TOK);
   static bool configured[64] = {false};
   int dev = 0;
@@ -453,18 +565,24 @@ int launch_variant(const GemmArgs& a, cudaStream_t stream) {
     configured[dev] = true;
   }
   CUtensorMap tmap_codes, tmap_packed;
-  if (!make_map(&tmap_codes, a.codes, static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.K), TOK, kBlockK,
-                CU_TENSOR_MAP_SWIZZLE_128B))
+  if (!make_map(&tmap_codes, a.codes, static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.K),
+                static_cast<uint32_t>(tok_tile), kBlockK, CU_TENSOR_MAP_SWIZZLE_128B))
     return SQ_ERR_DRIVER;
   if (!make_map(&tmap_packed, a.w_packed, static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 2), kBlockCh,
                 kBlockK / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
     return SQ_ERR_DRIVER;
   TcParams p;
   p.w_scales = a.w_scales; p.row_scales = a.row_scales; p.bias = a.bias; p.out = a.out;
-  p.acc_dump = a.acc_dump; p.status = device_status_word();
+  p.acc_dump = a.acc_dump; p.timeline = timeline; p.status = device_status_word();
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
-  p.tok_tiles = static_cast<int>((a.M + TOK - 1) / TOK);
+  p.tok_tile = tok_tile;
+  {  // first drain warp's share: a multiple of 32 columns (16 for the narrowest tile), capped by its capacity
+    const int cap = TOK == 160 ? 80 : TOK == 128 ? 64 : TOK == 64 ? 32 : 16;
+    const int want = TOK >= 64 ? ((tok_tile + 63) / 64) * 32 : 16;
+    p.half_cols = want < cap ? want : cap;
+  }
+  p.tok_tiles = static_cast<int>((a.M + tok_tile - 1) / tok_tile);
   p.k_blocks = static_cast<int>((a.K + kBlockK - 1) / kBlockK);
   p.out_dtype = a.out_dtype;
   const int tiles = p.ch_tiles * p.tok_tiles;
@@ -475,13 +593,13 @@ int launch_variant(const GemmArgs& a, cudaStream_t stream) {
 }
 
 template <int TOK, bool kGroup, bool kMagic>
-int launch_tok(const GemmArgs& a, cudaStream_t stream) {
+int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
   const bool eo = a.codes_layout == SQ_CODES_EVEN_ODD;
   const bool dump = a.acc_dump != nullptr;
   const bool bf16 = a.out_dtype == SQ_BF16;
 #define SQ_LAUNCH(EO, DUMP)                                                                          \
-  (bf16 ? launch_variant<TOK, kGroup, kMagic, EO, DUMP, __nv_bfloat16>(a, stream)                    \
-        : launch_variant<TOK, kGroup, kMagic, EO, DUMP, __half>(a, stream))
+  (bf16 ? launch_variant<TOK, kGroup, kMagic, EO, DUMP, __nv_bfloat16>(a, tok_tile, stream)          \
+        : launch_variant<TOK, kGroup, kMagic, EO, DUMP, __half>(a, tok_tile, stream))
   if (eo) return dump ? SQ_LAUNCH(true, true) : SQ_LAUNCH(true, false);
   return dump ? SQ_LAUNCH(false, true) : SQ_LAUNCH(false, false);
 #undef SQ_LAUNCH
@@ -489,13 +607,27 @@ int launch_tok(const GemmArgs& a, cudaStream_t stream) {
 
 template <bool kGroup, bool kMagic>
 int launch_mode(const GemmArgs& a, cudaStream_t stream) {
-  if (a.M <= 32) return launch_tok<32, kGroup, kMagic>(a, stream);
-  if (a.M <= 64) return launch_tok<64, kGroup, kMagic>(a, stream);
-  if (a.M <= 128) return launch_tok<128, kGroup, kMagic>(a, stream);
-  return launch_tok<256, kGroup, kMagic>(a, stream);
+  const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
+  const int t = pick_tok_tile(a.M, ch_tiles, sm_count());
+  if (t <= 32) return launch_tok<32, kGroup, kMagic>(a, t, stream);
+  if (t <= 64) return launch_tok<64, kGroup, kMagic>(a, t, stream);
+  if (t <= 128) return launch_tok<128, kGroup, kMagic>(a, t, stream);
+  return launch_tok<160, kGroup, kMagic>(a, t, stream);
 }
 
 }  // namespace
+
+int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t stream) {
+  int v = validate_gemm(a);
+  if (v != SQ_OK) return v;
+  if (timeline == nullptr) return SQ_ERR_NULL;
+  if (a.wscale_mode != SQ_WSCALE_GROUP_F16 || a.codes_layout != SQ_CODES_EVEN_ODD || a.out_dtype != SQ_BF16 || a.M <= 128)
+    return SQ_ERR_ENUM;
+  const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
+  int t = pick_tok_tile(a.M, ch_tiles, sm_count());
+  if (t <= 128) t = 160;
+  return launch_variant<160, true, true, true, false, __nv_bfloat16, true>(a, t, stream, timeline);
+}
 
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   int v = validate_gemm(a);

@@ -32,6 +32,8 @@ struct GemmArgs {
 int validate_gemm(const GemmArgs& a);
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
 int launch_gemm_check(const GemmArgs& a, cudaStream_t stream);
+// Group-scale bf16 GEMM with M > 128 only: same result, plus clock stamps of CTA 0's pipeline roles.
+int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t stream);
 
 // Device-side status word (0 = fine).  Written by kernels that gave up a bounded wait.
 int* device_status_word();

@@ -3,7 +3,7 @@
 // row scales.  One pass over global memory: each row lives in registers between the 128-bit
 // loads and the 64-bit code stores.
 //
-// Thread layout.  A row is covered by TPR threads (a power of two, 32..1024); thread t of the
+// Thread layout.  A row is covered by TPR threads (a power of two, 32..512); thread t of the
 // row owns the 8-element vectors t, t + TPR, t + 2 TPR, ... (VPT of them), so a warp reads 512
 // contiguous bytes per load.  A rotation block of B elements is B/8 consecutive vectors, i.e.
 // B/8 consecutive lanes of one warp: three butterfly stages run inside the thread (strides 1,
@@ -13,6 +13,13 @@
 // Arithmetic contract (what the CPU oracle does):
 //   token mode : s = max(amax / qmax, 1e-8);  code = clamp(rint(v / s))   (IEEE division, rint = half to even)
 //   static mode: f = gain / scale;            code = clamp(rint((v * inv_d) * f)),  row_scale = scale / gain
+// How it is computed without the slow paths:
+//   * v / s with one correctly rounded reciprocal r = RN(1/s) per row and two residual corrections per
+//     element, q0 = v r; q1 = q0 + (v - q0 s) r; q2 = q1 + (v - q1 s) r, each residual one exact FMA.  q1 is
+//     within one ulp of v / s, so q2 is the correctly rounded quotient (Markstein's theorem), i.e. the
+//     same float an IEEE division returns.
+//   * rint + clamp as clamp-then-add-1.5*2^23: the fp32 addition rounds to the nearest integer, ties to
+//     even, and leaves the code in the low byte of the sum's bit pattern.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -36,7 +43,13 @@ struct Vec8<__nv_bfloat16> {
       v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
   }
-  static __device__ __forceinline__ float round_trip(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+  // round two floats to bf16 and back with one packed conversion
+  static __device__ __forceinline__ void round_trip2(float& a, float& b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const uint32_t bits = *reinterpret_cast<const uint32_t*>(&h);
+    a = __uint_as_float(bits << 16);
+    b = __uint_as_float(bits & 0xFFFF0000u);
+  }
 };
 template <>
 struct Vec8<__half> {
@@ -50,7 +63,11 @@ struct Vec8<__half> {
       v[2 * i + 1] = f.y;
     }
   }
-  static __device__ __forceinline__ float round_trip(float f) { return __half2float(__float2half_rn(f)); }
+  static __device__ __forceinline__ void round_trip2(float& a, float& b) {
+    const float2 f = __half22float2(__floats2half2_rn(a, b));
+    a = f.x;
+    b = f.y;
+  }
 };
 
 struct PrepassParams {
@@ -70,10 +87,15 @@ struct PrepassParams {
   int mode, codes_layout, pack_int4;
 };
 
-__device__ __forceinline__ int clamp_code(int q, int qmax) { return max(-qmax, min(qmax, q)); }
+constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23
+
+// clamp to [-qmax, qmax], round to nearest even; the code is the low byte of the result
+__device__ __forceinline__ uint32_t round_code(float q, float qmax) {
+  return __float_as_uint(__fadd_rn(fminf(fmaxf(q, -qmax), qmax), kRoundMagic));
+}
 
 template <typename T, int VPT>
-__global__ void __launch_bounds__(VPT > 4 ? 512 : 1024) sq_prepass_kernel(const PrepassParams p) {
+__global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) {
   const int tpr = 1 << p.tpr_log2;
   const int t = threadIdx.x & (tpr - 1);
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> p.tpr_log2) + (threadIdx.x >> p.tpr_log2);
@@ -115,15 +137,19 @@ __global__ void __launch_bounds__(VPT > 4 ? 512 : 1024) sq_prepass_kernel(const 
       // strides 8, 16, ... across lanes: the lane whose bit is clear holds "left"
       for (int stage = 0; stage < p.rht_lanes_log2; ++stage) {
         const int lane_bit = 1 << stage;
-        const bool is_right = (threadIdx.x & lane_bit) != 0;
+        const float mine = (threadIdx.x & lane_bit) != 0 ? -1.0f : 1.0f;  // right: other - v, left: v + other
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float other = __shfl_xor_sync(0xffffffffu, v[j][i], lane_bit);
-          v[j][i] = is_right ? (other - v[j][i]) : (v[j][i] + other);
+          v[j][i] = fmaf(v[j][i], mine, other);
         }
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[j][i] = Vec8<T>::round_trip(v[j][i] * p.rht_norm);
+      for (int i = 0; i < 8; i += 2) {
+        v[j][i] = __fmul_rn(v[j][i], p.rht_norm);
+        v[j][i + 1] = __fmul_rn(v[j][i + 1], p.rht_norm);
+        Vec8<T>::round_trip2(v[j][i], v[j][i + 1]);
+      }
     }
   }
 
@@ -142,7 +168,9 @@ __global__ void __launch_bounds__(VPT > 4 ? 512 : 1024) sq_prepass_kernel(const 
 
   // scale: one number per row
   float divisor = 1.0f;     // token mode: codes = v / divisor
+  float reciprocal = 1.0f;  // RN(1 / divisor)
   float multiplier = 1.0f;  // static mode: codes = v * multiplier
+  const float qmax = static_cast<float>(p.qmax);
   if (p.mode == SQ_ACT_TOKEN) {
     float amax = 0.0f;
 #pragma unroll
@@ -162,6 +190,7 @@ __global__ void __launch_bounds__(VPT > 4 ? 512 : 1024) sq_prepass_kernel(const 
       for (int w = 0; w < warps_per_row; ++w) amax = fmaxf(amax, warp_max[first + w]);
     }
     divisor = fmaxf(__fdiv_rn(amax, static_cast<float>(p.qmax)), 1e-8f);
+    reciprocal = __frcp_rn(divisor);
     if (row_ok && t == 0) p.row_scales[row] = divisor;
   } else {
     int64_t stream;
@@ -181,27 +210,34 @@ __global__ void __launch_bounds__(VPT > 4 ? 512 : 1024) sq_prepass_kernel(const 
   for (int j = 0; j < VPT; ++j) {
     const int vec = j * tpr + t;
     if (vec >= vectors) continue;
-    int q[8];
+    uint32_t q[8];  // code in the low byte
     if (p.mode == SQ_ACT_TOKEN) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) q[i] = clamp_code(__float2int_rn(__fdiv_rn(v[j][i], divisor)), p.qmax);
+      for (int i = 0; i < 8; ++i) {
+        const float x = v[j][i];
+        const float q0 = __fmul_rn(x, reciprocal);
+        const float q1 = fmaf(fmaf(-q0, divisor, x), reciprocal, q0);
+        const float q2 = fmaf(fmaf(-q1, divisor, x), reciprocal, q1);
+        q[i] = round_code(q2, qmax);
+      }
     } else {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) q[i] = clamp_code(__float2int_rn(__fmul_rn(v[j][i], multiplier)), p.qmax);
+      for (int i = 0; i < 8; ++i) q[i] = round_code(__fmul_rn(v[j][i], multiplier), qmax);
     }
     if (p.pack_int4) {
       uint32_t word = 0;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) word |= static_cast<uint32_t>(q[i] & 0xF) << (4 * i);
+      for (int i = 0; i < 8; ++i) word |= (q[i] & 0xFu) << (4 * i);
       reinterpret_cast<uint32_t*>(p.codes)[row * vectors + vec] = word;
     } else {
       uint32_t lo, hi;
+      // low bytes of four words -> one word: two byte-permutes per pair, one to join
       if (p.codes_layout == SQ_CODES_EVEN_ODD) {
-        lo = (q[0] & 0xFF) | ((q[2] & 0xFF) << 8) | ((q[4] & 0xFF) << 16) | (static_cast<uint32_t>(q[6] & 0xFF) << 24);
-        hi = (q[1] & 0xFF) | ((q[3] & 0xFF) << 8) | ((q[5] & 0xFF) << 16) | (static_cast<uint32_t>(q[7] & 0xFF) << 24);
+        lo = __byte_perm(__byte_perm(q[0], q[2], 0x0040), __byte_perm(q[4], q[6], 0x0040), 0x5410);
+        hi = __byte_perm(__byte_perm(q[1], q[3], 0x0040), __byte_perm(q[5], q[7], 0x0040), 0x5410);
       } else {
-        lo = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | (static_cast<uint32_t>(q[3] & 0xFF) << 24);
-        hi = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | (static_cast<uint32_t>(q[7] & 0xFF) << 24);
+        lo = __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+        hi = __byte_perm(__byte_perm(q[4], q[5], 0x0040), __byte_perm(q[6], q[7], 0x0040), 0x5410);
       }
       reinterpret_cast<uint2*>(p.codes)[row * vectors + vec] = make_uint2(lo, hi);
     }
@@ -216,7 +252,9 @@ static cudaError_t launch_for_type(const PrepassParams& p, int vpt, dim3 grid, d
     case 3: sq_prepass_kernel<T, 3><<<grid, block, 0, stream>>>(p); break;
     case 4: sq_prepass_kernel<T, 4><<<grid, block, 0, stream>>>(p); break;
     case 5: sq_prepass_kernel<T, 5><<<grid, block, 0, stream>>>(p); break;
-    default: sq_prepass_kernel<T, 6><<<grid, block, 0, stream>>>(p); break;
+    case 6: sq_prepass_kernel<T, 6><<<grid, block, 0, stream>>>(p); break;
+    case 7: sq_prepass_kernel<T, 7><<<grid, block, 0, stream>>>(p); break;
+    default: sq_prepass_kernel<T, 8><<<grid, block, 0, stream>>>(p); break;
   }
   return cudaGetLastError();
 }
@@ -246,10 +284,11 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
     if (streams <= 0 || span == 0) return SQ_ERR_SHAPE;
     if (span < 0 && (seq_tokens <= 0 || -span >= seq_tokens || streams != 2)) return SQ_ERR_SHAPE;
   }
-  // threads per row: smallest power of two >= 32 that leaves at most 6 vectors per thread
+  // threads per row: smallest power of two in [32, 512] that leaves at most 4 vectors per thread
+  // (up to 8 vectors per thread beyond K = 16384)
   const int64_t vectors = K >> 3;
   int tpr_log2 = 5;
-  while (((vectors + (int64_t{1} << tpr_log2) - 1) >> tpr_log2) > 6) ++tpr_log2;
+  while (tpr_log2 < 9 && ((vectors + (int64_t{1} << tpr_log2) - 1) >> tpr_log2) > 4) ++tpr_log2;
   const int tpr = 1 << tpr_log2;
   const int vpt = static_cast<int>((vectors + tpr - 1) / tpr);
   const int threads = tpr > 256 ? tpr : 256;

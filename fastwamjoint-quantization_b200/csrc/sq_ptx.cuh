@@ -159,6 +159,23 @@ __device__ __forceinline__ void tmem_st_32x32b_x16_fill(uint32_t taddr, uint32_t
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st_32x32b_x32_fill(uint32_t taddr, uint32_t v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+      "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+      ::"r"(taddr), "r"(v)
+      : "memory");
+}
+// chunk-size generic forms
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x32b_x16(taddr, r); }
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_32x32b_x32(taddr, r); }
+template <int kCols>
+__device__ __forceinline__ void tmem_st_fill(uint32_t taddr, uint32_t v) {
+  if (kCols == 32) tmem_st_32x32b_x32_fill(taddr, v);
+  else tmem_st_32x32b_x16_fill(taddr, v);
+}
+
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128
 // bytes with the 128-byte swizzle (what a TMA box with inner extent 128 B and

@@ -26,7 +26,7 @@ def _stream():
 
 def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None, rht_block: int = 128,
             act_scale=None, gains=None, span: int = 1, streams: int = 1, seq_tokens: int | None = None,
-            codes_layout: int = _lib.CODES_EVEN_ODD, pack_int4: bool = False):
+            codes_layout: int = _lib.CODES_EVEN_ODD, pack_int4: bool = False, out=None):
     """Run the fused activation pre-pass.  ``x`` is [..., tokens, K] bf16/fp16.
     Returns ``(codes, row_scales)``: int8 [rows, K] (or uint8 [rows, K/2] when
     ``pack_int4``) and fp32 [rows]."""
@@ -34,9 +34,12 @@ def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None,
     x = x.contiguous()
     k = x.shape[-1]
     rows = x.numel() // k
-    codes = torch.empty((rows, k // 2) if pack_int4 else (rows, k), device=x.device,
-                        dtype=torch.uint8 if pack_int4 else torch.int8)
-    row_scales = torch.empty((rows,), device=x.device, dtype=torch.float32)
+    if out is not None:
+        codes, row_scales = out
+    else:
+        codes = torch.empty((rows, k // 2) if pack_int4 else (rows, k), device=x.device,
+                            dtype=torch.uint8 if pack_int4 else torch.int8)
+        row_scales = torch.empty((rows,), device=x.device, dtype=torch.float32)
     with torch.cuda.device(x.device):
         status = _lib.load_library().sq_prepass(
             x.data_ptr(), _DTYPES[x.dtype], rows, k, int(abits),
@@ -50,7 +53,7 @@ def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None,
 
 def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_scales: torch.Tensor, bias,
          *, out_dtype: torch.dtype, codes_layout: int = _lib.CODES_EVEN_ODD, want_accumulators: bool = False,
-         check_kernel: bool = False):
+         check_kernel: bool = False, out: torch.Tensor | None = None):
     """codes int8 [M, K] x packed uint8 [N, K/2] -> [M, N] in ``out_dtype``.
     ``w_scales`` fp32 [N] selects the per-channel form, fp16 [N, K/128] the group form.
     ``check_kernel`` runs the CUDA-core cross-check kernel instead of the tensor-core one (tests only)."""
@@ -58,7 +61,8 @@ def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_
     m, k = codes.shape
     n = packed.shape[0]
     group = w_scales.dtype == torch.float16
-    out = torch.empty((m, n), device=codes.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty((m, n), device=codes.device, dtype=out_dtype)
     acc = None
     if want_accumulators:
         acc = torch.empty((m, n, k // 128 if group else 1), device=codes.device, dtype=torch.int32)
@@ -74,8 +78,10 @@ def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_
 
 def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, *, abits: int, mode: str,
            inverse=None, signs=None, rht_block: int = 128, act_scales=None, gains=None, call: int = 0,
-           span: int = 1, streams: int = 1) -> torch.Tensor:
-    """One whole quantized linear (pre-pass + GEMM) through ``sq_linear``."""
+           span: int = 1, streams: int = 1, out: torch.Tensor | None = None,
+           workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """One whole quantized linear (pre-pass + GEMM) through ``sq_linear``.  ``out`` and ``workspace``
+    (uint8, at least ``sq_workspace_bytes(rows, K)``) may be passed to reuse buffers across calls."""
     _require_cuda(x, "x")
     x = x.contiguous()
     k = x.shape[-1]
@@ -83,8 +89,14 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
     n = packed.shape[0]
     lib = _lib.load_library()
     nbytes = lib.sq_workspace_bytes(rows, k)
-    workspace = torch.empty((max(nbytes, 1),), device=x.device, dtype=torch.uint8)
-    out = torch.empty((*x.shape[:-1], n), device=x.device, dtype=x.dtype)
+    if workspace is None:
+        workspace = torch.empty((max(nbytes, 1),), device=x.device, dtype=torch.uint8)
+    elif workspace.numel() < nbytes or workspace.dtype != torch.uint8 or not workspace.is_cuda:
+        raise RuntimeError("workspace must be a CUDA uint8 tensor of at least sq_workspace_bytes(rows, K) bytes.")
+    if out is None:
+        out = torch.empty((*x.shape[:-1], n), device=x.device, dtype=x.dtype)
+    elif out.shape != (*x.shape[:-1], n) or out.dtype != x.dtype or not out.is_contiguous():
+        raise RuntimeError("out must be a contiguous tensor of shape x.shape[:-1] + (N,) in x's dtype.")
     group = w_scales.dtype == torch.float16
     calls = 0 if act_scales is None else act_scales.numel()
     with torch.cuda.device(x.device):
@@ -97,6 +109,27 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
             _ptr(bias), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
     _lib.check(status, "sq_linear")
     return out
+
+
+TIMELINE_ROLES = ("tma_issue", "unpack_start", "unpack_done", "acc_free", "mma_issue", "drain_start",
+                  "acc_released", "drain_done")
+
+
+def gemm_timeline(codes, packed, w_scales, row_scales, bias):
+    """``gemm`` for the group-scale bf16 case plus the pipeline timeline of thread block 0: returns
+    ``(out, stamps)`` with ``stamps`` an int64 [8, 512] tensor of SM clock values (0 = slot not reached);
+    rows are named by ``TIMELINE_ROLES``."""
+    _require_cuda(codes, "codes")
+    m, k = codes.shape
+    n = packed.shape[0]
+    out = torch.empty((m, n), device=codes.device, dtype=torch.bfloat16)
+    stamps = torch.zeros((8, 512), device=codes.device, dtype=torch.int64)
+    with torch.cuda.device(codes.device):
+        status = _lib.load_library().sq_gemm_timeline(codes.data_ptr(), packed.data_ptr(), w_scales.data_ptr(),
+                                                      row_scales.data_ptr(), _ptr(bias), out.data_ptr(), m, n, k,
+                                                      stamps.data_ptr(), _stream())
+    _lib.check(status, "sq_gemm_timeline")
+    return out, stamps
 
 
 def device_status() -> int:
