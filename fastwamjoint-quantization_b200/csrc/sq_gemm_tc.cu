@@ -1,7 +1,7 @@
 // W4A8 / W4A4 GEMM on the 5th-generation tensor cores: out[m, n] = sum_k a[m, k] * w[n, k].
 //
 // The MMA runs "weights as rows": the UMMA M dimension (TMEM lanes) is 128 output channels,
-// the UMMA N dimension (TMEM columns) is up to 160 tokens.  A TMEM lane therefore belongs to ONE
+// the UMMA N dimension (TMEM columns) is up to 128 tokens.  A TMEM lane therefore belongs to ONE
 // output channel, so the per-group weight scale is a per-thread scalar when the accumulator is
 // drained, and small token counts map to a small UMMA N instead of a wasted 128-row tile.
 //
@@ -15,7 +15,8 @@
 //   warps 8-15    drain: tcgen05.ld the int32 accumulator of one weight group, convert, multiply by
 //                 the group scale, add into fp32 sums in registers; after the last group apply the row
 //                 scale and bias and store bf16/fp16
-// Two TMEM accumulators of TOK columns alternate, so the MMAs of group g+1 overlap the drain of g.
+// TMEM holds a ring of 3 or 4 accumulators, so the MMA warp runs ahead of the drain; the drain in turn
+// issues the TMEM loads of group g+1 while it does the arithmetic of group g.
 //
 // Every mbarrier wait is time-bounded (see sq_ptx.cuh); a wait that gives up sets the CTA's abort
 // flag and the device status word, all roles leave their loops, TMEM is released, the kernel returns.
@@ -37,24 +38,25 @@ namespace {
 constexpr int kBlockCh = 128;  // output channels per tile = UMMA M = TMEM lanes
 constexpr int kBlockK = 128;   // int8 K elements per stage = one swizzle row = one weight group
 constexpr int kUmmaK = 32;     // K of one kind::i8 instruction
-constexpr int kThreads = 512;
+constexpr int kThreads = 768;  // 4 control + 4 unpack + 16 drain warps
 constexpr uint32_t kPackedBytes = kBlockCh * kBlockK / 2;  // 8 KiB
 constexpr uint32_t kWBytes = kBlockCh * kBlockK;           // 16 KiB
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
-constexpr uint32_t kMagicBits = 0x4B400000u;               // float 12582912 = 1.5 * 2^23
-constexpr float kMagicFloat = 12582912.0f;
 
 // Timeline capture (debug entry point sq_gemm_timeline): CTA 0 stamps clock64() per K block.
 constexpr int kTraceSlots = 512;
 enum TraceRole { kTrTmaIssue = 0, kTrConvStart, kTrConvDone, kTrMmaAccFree, kTrMmaIssue, kTrDrainStart,
-                 kTrDrainRelease, kTrDrainDone, kTraceRoles };
+                 kTrDrainRelease, kTrDrainDone, kTrMmaCommitted, kTraceRoles };
+
+constexpr uint32_t kMagicBits = 0x4B400000u;  // bit pattern of the float 12582912 = 1.5 * 2^23
+constexpr float kMagicFloat = 12582912.0f;
 
 constexpr int kNumConverterWarps = 4;
-constexpr int kNumDrainWarps = 8;
+constexpr int kNumDrainWarps = 16;  // four per TMEM lane quarter, each owns a slice of the token columns
 
 __host__ __device__ constexpr int stages_for(int tok) {
   // shared memory per stage: unpacked weights + codes + packed weights
-  return tok == 160 ? 5 : tok == 128 ? 5 : tok == 64 ? 7 : 8;
+  return tok == 128 ? 5 : tok == 64 ? 7 : 8;
 }
 __host__ __device__ constexpr uint32_t stage_bytes(int tok) { return kWBytes + tok * kBlockK + kPackedBytes; }
 __host__ __device__ constexpr uint32_t smem_bytes_for(int tok) {
@@ -72,7 +74,7 @@ struct TcParams {
   int64_t M, N, K;
   int ch_tiles, tok_tiles, k_blocks;
   int tok_tile;   // tokens per tile at run time: a multiple of 16, <= TOK
-  int half_cols;  // columns drained by the first warp of each lane quarter (the second takes the rest)
+  int slice_cols;  // token columns per drain warp: drain warp j of a lane quarter owns [j, j + 1) * slice_cols
   int out_dtype;
 };
 
@@ -94,29 +96,6 @@ __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.al
 template <int kRegs>
 __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs)); }
 
-// Two fp32 values in one 64-bit register, for the packed add / fma of sm_100.
-__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  uint32_t a, b;
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
-  lo = __uint_as_float(a);
-  hi = __uint_as_float(b);
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-
 __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code) {
   *abort_flag = 1;
   atomicCAS(status, 0, code);
@@ -125,28 +104,25 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
 // TOK    capacity in tokens of one tile (TMEM columns per accumulator, rows of a codes stage); the
 //        tile actually used, p.tok_tile <= TOK, is chosen per call so the tiles fill the SMs evenly
 // kGroup one accumulator per 128-K weight group (fp16 scales [N, K/128]); otherwise one per tile (fp32 [N])
-// kMagic group mode only: TMEM accumulators start at the bit pattern of 1.5 * 2^23, so the drained word
-//        re-read as a float is 12582912 + acc exactly and the int->float conversion is one subtraction
 // kEvenOdd codes are stored even-k-first inside each run of 8 (no byte interleave needed when unpacking)
 // kDump  also write the exact integer accumulators
-template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
+template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TcParams p) {
-  static_assert(!kMagic || kGroup, "the magic-number drain needs |16 acc| < 2^22, true only per 128-K group");
   constexpr int S = stages_for(TOK);
   constexpr uint32_t kXBytes = TOK * kBlockK;
-  // Each of the two drain warps of a lane quarter owns up to kColsPerHalf token columns and reads them
-  // with loads that are all in flight at once (kFull 32-column loads plus one 16-column load when
-  // kTail): a tcgen05.ld round trip costs a few hundred cycles, so the loads of one accumulator must
-  // overlap each other, not follow each other.  80 columns + 80 fp32 sums per thread is what fits the
-  // register file next to the other roles, hence 160 tokens per tile at most.
-  constexpr int kColsPerHalf = TOK == 160 ? 80 : TOK == 128 ? 64 : TOK == 64 ? 32 : 16;
-  constexpr int kFull = kColsPerHalf / 32;
-  constexpr bool kTail = (kColsPerHalf % 32) != 0;
-  constexpr uint32_t kBufStride = TOK > 128 ? 256 : TOK > 64 ? 128 : TOK;  // TMEM columns between accumulators
-  constexpr uint32_t kTmemCols = 2 * kBufStride < 32 ? 32 : 2 * kBufStride;
-  static_assert(TOK == 160 || TOK == 128 || TOK == 64 || TOK == 32, "tile capacities");
+  // Each of the four drain warps of a lane quarter owns up to kCols token columns of an accumulator and
+  // reads them with ONE tcgen05.ld (a TMEM load costs a few hundred cycles whatever its width, and the
+  // loads of one warp do not overlap each other).  While some warps of a scheduler wait for their load,
+  // the others convert and accumulate: four warps per scheduler hide the TMEM and barrier round trips.
+  constexpr int kCols = TOK / 4 < 16 ? 16 : TOK / 4;  // 32 or 16 columns per drain warp
+  // TMEM holds a ring of four accumulators so the MMA warp can run ahead of the drain by three groups
+  constexpr uint32_t kAccBufs = 4;
+  constexpr int kMmaWarps = kGroup ? 3 : 1;
+  constexpr uint32_t kBufStride = 128;  // TMEM columns between accumulators
+  constexpr uint32_t kTmemCols = 512;
+  static_assert(TOK == 128 || TOK == 64 || TOK == 32, "tile capacities");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -157,9 +133,9 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   const uint32_t bar_full = bars;                     // [S] TMA landed (tx bytes)
   const uint32_t bar_wfull = bars + 8 * S;            // [S] converters wrote W[s]
   const uint32_t bar_empty = bars + 16 * S;           // [S] MMAs reading stage s retired
-  const uint32_t bar_acc_full = bars + 24 * S;        // [2]
-  const uint32_t bar_acc_empty = bars + 24 * S + 16;  // [2]
-  const uint32_t tmem_slot = bars + 24 * S + 32;
+  const uint32_t bar_acc_full = bars + 24 * S;        // [kAccBufs]
+  const uint32_t bar_acc_empty = bars + 24 * S + 32;  // [kAccBufs]
+  const uint32_t tmem_slot = bars + 24 * S + 64;
   const uint32_t abort_slot = tmem_slot + 4;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + (abort_slot - smem_base));
@@ -174,7 +150,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       mbar_init(bar_wfull + 8 * s, kNumConverterWarps);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < static_cast<int>(kAccBufs); ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
       mbar_init(bar_acc_empty + 8 * b, kNumDrainWarps);
     }
@@ -203,7 +179,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   if (warp < 4) {
     // ------------------------------------------------------------------ control warpgroup
     reg_dec<32>();
-    if (warp == 0 && lane == 0) {
+    // Both roles keep the whole warp in the loop and pick the issuing thread with elect.sync: TMA and
+    // tcgen05 instructions take warp-uniform operands, and only an elected region lets the compiler keep
+    // them in uniform registers (a plain `lane == 0` branch costs about a hundred cycles per instruction).
+    if (warp == 0) {
       // TMA producer
       uint32_t it = 0;
       bool ok = true;
@@ -213,18 +192,28 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
           const uint32_t s = it % S, phase = (it / S) & 1u;
           if (!mbar_wait_bounded(bar_empty + 8 * s, phase ^ 1u, abort_flag, kWaitLimitNs)) {
-            report_timeout(p.status, abort_flag, 9001);
+            if (lane == 0) report_timeout(p.status, abort_flag, 9001);
             ok = false;
             break;
           }
-          stamp(kTrTmaIssue, it);
-          mbar_arrive_expect_tx(bar_full + 8 * s, static_cast<uint32_t>(p.tok_tile) * kBlockK + kPackedBytes);
-          tma_load_2d(p_ring + s * kPackedBytes, &tmap_packed, kb * (kBlockK / 2), ch0, bar_full + 8 * s);
-          tma_load_2d(x_ring + s * kXBytes, &tmap_codes, kb * kBlockK, tok0, bar_full + 8 * s);
+          if (elect_one()) {
+            stamp(kTrTmaIssue, it);
+            // The codes land on the barrier the MMA warps wait on (together with the unpack warps'
+            // arrivals), the packed weights on the barrier the unpack warps wait on.  The expect_tx on
+            // bar_wfull is issued before the packed load, so no unpack warp can arrive for this phase first.
+            mbar_expect_tx(bar_wfull + 8 * s, static_cast<uint32_t>(p.tok_tile) * kBlockK);
+            mbar_arrive_expect_tx(bar_full + 8 * s, kPackedBytes);
+            tma_load_2d(x_ring + s * kXBytes, &tmap_codes, kb * kBlockK, tok0, bar_wfull + 8 * s);
+            tma_load_2d(p_ring + s * kPackedBytes, &tmap_packed, kb * (kBlockK / 2), ch0, bar_full + 8 * s);
+          }
+          __syncwarp();
         }
       }
-    } else if (warp == 1 && lane == 0) {
-      // MMA issuer
+    } else if (warp <= kMmaWarps) {
+      // MMA issuers.  Group mode: warps 1..3 take the groups round-robin (a group is one K block with its
+      // own accumulator), so the barrier round trips of one group overlap the issue of the next two.
+      // Channel mode: warp 1 alone, because all K blocks of a tile add into one accumulator in order.
+      const uint32_t mine = static_cast<uint32_t>(warp - 1);
       uint32_t it = 0, git = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -234,42 +223,48 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const uint32_t umma_n = static_cast<uint32_t>((tok_count + 15) & ~15);
         const uint32_t idesc = umma_idesc_i8(kBlockCh, umma_n);
         for (int g = 0; g < groups && ok; ++g, ++git) {
-          const uint32_t buf = git & 1u, aphase = (git >> 1) & 1u;
+          if (kGroup && git % kMmaWarps != mine) {
+            it += blocks_per_group;
+            continue;
+          }
+          const uint32_t buf = git % kAccBufs, aphase = (git / kAccBufs) & 1u;
           if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
-            report_timeout(p.status, abort_flag, 9002);
+            if (lane == 0) report_timeout(p.status, abort_flag, 9002);
             ok = false;
             break;
           }
-          tc_fence_after_sync();
-          stamp(kTrMmaAccFree, git);
+          if (warp == 1 && lane == 0) stamp(kTrMmaAccFree, git);
           const uint32_t tmem_d = tmem_base + buf * kBufStride;
           for (int kb = 0; kb < blocks_per_group; ++kb, ++it) {
             const uint32_t s = it % S, phase = (it / S) & 1u;
-            if (!mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs) ||
-                !mbar_wait_bounded(bar_wfull + 8 * s, phase, abort_flag, kWaitLimitNs)) {
-              report_timeout(p.status, abort_flag, 9003);
+            if (!mbar_wait_bounded(bar_wfull + 8 * s, phase, abort_flag, kWaitLimitNs)) {
+              if (lane == 0) report_timeout(p.status, abort_flag, 9003);
               ok = false;
               break;
             }
             tc_fence_after_sync();
-            stamp(kTrMmaIssue, it);
-            const uint64_t desc_a = umma_desc_k128(w_ring + s * kWBytes);
-            const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
+            if (warp == 1 && lane == 0) stamp(kTrMmaIssue, it);
+            if (elect_one()) {
+              const uint64_t desc_a = umma_desc_k128(w_ring + s * kWBytes);
+              const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-              const uint32_t accumulate = kMagic ? 1u : ((kb > 0 || k > 0) ? 1u : 0u);
-              // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in the (address >> 4) field
-              umma_i8(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
+              for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in the (address >> 4) field
+                umma_i8(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
+              }
+              umma_commit(bar_empty + 8 * s);  // frees the stage when these MMAs retire
+              if (kb + 1 == blocks_per_group) umma_commit(bar_acc_full + 8 * buf);
             }
-            umma_commit(bar_empty + 8 * s);
+            __syncwarp();
           }
-          if (ok) umma_commit(bar_acc_full + 8 * buf);
+          if (warp == 1 && lane == 0) stamp(kTrMmaCommitted, git);
         }
       }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ converter warpgroup
-    reg_dec<56>();
+    reg_dec<48>();
     const int ctid = threadIdx.x - 128;  // 0..127
     uint32_t it = 0;
     bool ok = true;
@@ -284,20 +279,24 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (ctid == 0) stamp(kTrConvStart, it);
         const uint32_t src = p_ring + s * kPackedBytes;
         const uint32_t dst = w_ring + s * kWBytes;
+        // all four 16-byte loads first, then the unpack and the eight stores: the loads overlap
+        uint32_t win[4][4];
 #pragma unroll
         for (int u4 = 0; u4 < 4; ++u4) {
           const int unit = u4 * 128 + ctid;  // 16 packed bytes = 32 k of one channel row
-          const int row = unit >> 2, c = unit & 3;
-          uint32_t w0, w1, w2, w3;
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                       : "=r"(win[u4][0]), "=r"(win[u4][1]), "=r"(win[u4][2]), "=r"(win[u4][3])
                        : "r"(src + unit * 16));
+        }
+#pragma unroll
+        for (int u4 = 0; u4 < 4; ++u4) {
+          const int unit = u4 * 128 + ctid;
+          const int row = unit >> 2, c = unit & 3;
           uint32_t o[8];
-          const uint32_t win[4] = {w0, w1, w2, w3};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint32_t lo = (win[i] << 4) & 0xF0F0F0F0u;  // 16 * nibble of even k, as int8
-            const uint32_t hi = win[i] & 0xF0F0F0F0u;         // 16 * nibble of odd k
+            const uint32_t lo = (win[u4][i] << 4) & 0xF0F0F0F0u;  // 16 * nibble of even k, as int8
+            const uint32_t hi = win[u4][i] & 0xF0F0F0F0u;         // 16 * nibble of odd k
             if (kEvenOdd) {
               o[2 * i] = lo;
               o[2 * i + 1] = hi;
@@ -309,9 +308,9 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           const uint32_t row_base = dst + row * 128;
           const uint32_t sw = static_cast<uint32_t>(row & 7);
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (((2 * c) ^ sw) << 4)),
-                       "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+                       "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]));
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (((2 * c + 1) ^ sw) << 4)),
-                       "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+                       "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
         }
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
@@ -321,29 +320,21 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ drain warpgroups
-    reg_inc<208>();
-    const int dwarp = warp - 8;           // 0..7
+    reg_inc<96>();
+    const int dwarp = warp - 8;           // 0..15
     const int quarter = warp & 3;         // TMEM lane quarter this warp may address
-    const int half = dwarp >> 2;          // which share of the token columns (two warps per lane quarter)
+    const int slice = dwarp >> 2;         // which slice of the token columns (four warps per lane quarter)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int ch_in_tile = quarter * 32 + lane;
 
-    // hand both accumulators to the MMA warp (after writing the magic start value, if used)
-    const int my_col0 = half * p.half_cols;  // first token column of this warp inside a tile
+    // hand every accumulator of the ring to the MMA warp
+    const int my_col0 = slice * p.slice_cols;  // first token column of this warp inside a tile
 #pragma unroll
-    for (int b = 0; b < 2; ++b) {
-      if (kMagic) {
-#pragma unroll
-        for (int c = 0; c < kFull; ++c)
-          tmem_st_fill<32>(tmem_base + lane_addr + b * kBufStride + my_col0 + c * 32, kMagicBits);
-        if (kTail) tmem_st_fill<16>(tmem_base + lane_addr + b * kBufStride + my_col0 + kFull * 32, kMagicBits);
-        tmem_wait_st();
-      }
+    for (int b = 0; b < static_cast<int>(kAccBufs); ++b) {
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);
     }
-    const uint64_t neg_magic2 = pack2(__float_as_uint(-kMagicFloat), __float_as_uint(-kMagicFloat));
     const __half* scale_row = static_cast<const __half*>(p.w_scales);
 
     uint32_t git = 0;
@@ -353,15 +344,13 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
       const int64_t left = p.M - tok0;
       const int tok_count = left < p.tok_tile ? static_cast<int>(left) : p.tok_tile;
-      const int my_limit = half == 0 ? p.half_cols : p.tok_tile - p.half_cols;
-      const int my_cols = min(max(tok_count - my_col0, 0), my_limit);  // real tokens in my share
-      const bool tail_on = kTail && my_cols > kFull * 32;  // warp-uniform
+      const int my_cols = min(max(tok_count - my_col0, 0), p.slice_cols);  // real tokens in my slice
       const int64_t n = ch0 + ch_in_tile;
       const bool n_ok = n < p.N;
 
-      uint64_t sums[kColsPerHalf / 2];  // fp32 pairs: columns (2j, 2j+1)
+      float sums[kCols];
 #pragma unroll
-      for (int i = 0; i < kColsPerHalf / 2; ++i) sums[i] = 0ull;
+      for (int i = 0; i < kCols; ++i) sums[i] = 0.0f;
 
       // group scales are fetched two groups ahead as raw fp16 bits and converted when used, so the
       // global-load latency never sits in front of a drain
@@ -372,7 +361,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       }
 
       for (int g = 0; g < groups && ok; ++g, ++git) {
-        const uint32_t buf = git & 1u, aphase = (git >> 1) & 1u;
+        const uint32_t buf = git % kAccBufs, aphase = (git / kAccBufs) & 1u;
         float scale = 0.0625f;  // the unpacked weights are 16 x the int4 value
         if (kGroup) {
           scale = __half2float(__ushort_as_half(raw0)) * 0.0625f;
@@ -380,7 +369,6 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           if (g + 2 < groups && n_ok)
             raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + g + 2);
         }
-        const uint64_t scale2 = pack2(__float_as_uint(scale), __float_as_uint(scale));
         if (!mbar_wait_bounded(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9005);
           ok = false;
@@ -388,58 +376,37 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         }
         tc_fence_after_sync();
         if (threadIdx.x == 256) stamp(kTrDrainStart, git);
+        uint32_t r[kCols];
         const uint32_t taddr = tmem_base + lane_addr + buf * kBufStride + my_col0;
-        uint32_t r[kFull > 0 ? kFull : 1][32];
-        uint32_t rt[16];
-#pragma unroll
-        for (int c = 0; c < kFull; ++c)
-          if (c * 32 < my_cols) tmem_ld_chunk(taddr + c * 32, r[c]);
-        if (tail_on) tmem_ld_chunk(taddr + kFull * 32, rt);
-        if (my_cols > 0) tmem_wait_ld();
-        if (kMagic) {
-#pragma unroll
-          for (int c = 0; c < kFull; ++c)
-            if (c * 32 < my_cols) tmem_st_fill<32>(taddr + c * 32, kMagicBits);
-          if (tail_on) tmem_st_fill<16>(taddr + kFull * 32, kMagicBits);
-          if (my_cols > 0) tmem_wait_st();
+        if (my_cols > 0) {
+          tmem_ld_chunk(taddr, r);
+          tmem_wait_ld();
         }
-        // the accumulator is in registers (and re-armed): give it back before doing the arithmetic
+        // the accumulator is in registers: give it back before doing the arithmetic
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
         if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
-        auto accumulate = [&](const uint32_t* regs, int width, int col0) {
+        if (my_cols > 0) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            if (i < width / 2) {
-              uint64_t value2;
-              if (kMagic) {
-                value2 = add2(pack2(regs[2 * i], regs[2 * i + 1]), neg_magic2);
-              } else {
-                value2 = pack2(__float_as_uint(static_cast<float>(static_cast<int32_t>(regs[2 * i]))),
-                               __float_as_uint(static_cast<float>(static_cast<int32_t>(regs[2 * i + 1]))));
-              }
-              sums[col0 / 2 + i] = fma2(value2, scale2, sums[col0 / 2 + i]);
-            }
+          for (int i = 0; i < kCols; ++i) {
+            // group mode: |16 acc| < 2^22 inside one 128-K group, so adding the bit pattern of 1.5 * 2^23
+            // gives the float 12582912 + 16 acc exactly: int -> float is an integer add and a float
+            // subtract (full rate) instead of a conversion instruction (a sixteenth of the rate)
+            const float value = kGroup ? __fadd_rn(__uint_as_float(r[i] + kMagicBits), -kMagicFloat)
+                                       : static_cast<float>(static_cast<int32_t>(r[i]));
+            sums[i] = fmaf(value, scale, sums[i]);
           }
           if (kDump) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (i < width) {
-                const int col = col0 + i;
-                if (n_ok && col < my_cols) {
-                  const int64_t m = tok0 + my_col0 + col;
-                  const int32_t acc16 = kMagic ? static_cast<int32_t>(regs[i] - kMagicBits) : static_cast<int32_t>(regs[i]);
-                  p.acc_dump[(m * p.N + n) * groups + g] = acc16 >> 4;
-                }
+            for (int i = 0; i < kCols; ++i) {
+              if (n_ok && i < my_cols) {
+                const int64_t m = tok0 + my_col0 + i;
+                p.acc_dump[(m * p.N + n) * groups + g] = static_cast<int32_t>(r[i]) >> 4;
               }
             }
           }
-        };
-#pragma unroll
-        for (int c = 0; c < kFull; ++c)
-          if (c * 32 < my_cols) accumulate(r[c], 32, c * 32);
-        if (tail_on) accumulate(rt, 16, kFull * 32);
+        }
         if (threadIdx.x == 256) stamp(kTrDrainDone, git);
       }
       if (!ok) break;
@@ -454,7 +421,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const float* rs_ptr = p.row_scales + tok0 + my_col0;
         const int64_t m0 = tok0 + my_col0;
 #pragma unroll
-        for (int j = 0; j < kColsPerHalf / 4; ++j) {
+        for (int j = 0; j < kCols / 4; ++j) {
           if (4 * j < my_cols) {
             float rs[4];
             if (4 * j + 4 <= my_cols) {
@@ -464,9 +431,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 #pragma unroll
               for (int e = 0; e < 4; ++e) rs[e] = (4 * j + e < my_cols) ? __ldg(rs_ptr + 4 * j + e) : 0.0f;
             }
-            float acc[4];
-            unpack2(sums[2 * j], acc[0], acc[1]);
-            unpack2(sums[2 * j + 1], acc[2], acc[3]);
+            const float acc[4] = {sums[4 * j], sums[4 * j + 1], sums[4 * j + 2], sums[4 * j + 3]};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               if (4 * j + e < my_cols) {
@@ -533,16 +498,17 @@ int sm_count() {
   return cached[dev] > 0 ? cached[dev] : 148;
 }
 
-// Tokens per tile: a multiple of 16 up to 160 (two drain warps x 80 columns held in registers at once).  A tile costs about max(t, 96) + 8 "column units" (below
-// ~96 tokens the int4 unpack, not the MMA, sets the pace); the kernel runs ceil(tiles / SMs) waves.
+// Tokens per tile: a multiple of 16 up to 128 (four drain warps x 32 columns per TMEM lane quarter).
+// Measured on B200 a 128-K group costs a fixed part (barrier and TMEM round trips, int4 unpack) plus a part
+// proportional to the tile width, roughly 150 + t "column units"; the kernel runs ceil(tiles / SMs) waves.
 int pick_tok_tile(int64_t M, int ch_tiles, int sms) {
   if (M <= 16) return 16;
   int best = 16;
   double best_cost = 1e30;
-  for (int t = 16; t <= 160; t += 16) {
+  for (int t = 16; t <= 128; t += 16) {
     const int64_t tiles = static_cast<int64_t>(ch_tiles) * ((M + t - 1) / t);
     const int64_t waves = (tiles + sms - 1) / sms;
-    const double cost = static_cast<double>(waves) * ((t > 96 ? t : 96) + 8);
+    const double cost = static_cast<double>(waves) * (t + 150);
     if (cost <= best_cost) {  // ties go to the wider tile
       best_cost = cost;
       best = t;
@@ -552,9 +518,9 @@ int pick_tok_tile(int64_t M, int ch_tiles, int sms) {
   return best;
 }
 
-template <int TOK, bool kGroup, bool kMagic, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
+template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
 int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long long* timeline = nullptr) {
-  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kMagic, kEvenOdd, kDump, OutT, kTrace>;
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace>;
   constexpr uint32_t smem = smem_bytes_for(TOK);
   static bool configured[64] = {false};
   int dev = 0;
@@ -577,10 +543,10 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
   p.tok_tile = tok_tile;
-  {  // first drain warp's share: a multiple of 32 columns (16 for the narrowest tile), capped by its capacity
-    const int cap = TOK == 160 ? 80 : TOK == 128 ? 64 : TOK == 64 ? 32 : 16;
-    const int want = TOK >= 64 ? ((tok_tile + 63) / 64) * 32 : 16;
-    p.half_cols = want < cap ? want : cap;
+  {  // a quarter of the tile rounded up to 16 columns, at most a drain warp's register capacity
+    const int cap = TOK / 4 < 16 ? 16 : TOK / 4;
+    const int want = ((tok_tile + 63) / 64) * 16;
+    p.slice_cols = want < cap ? want : cap;
   }
   p.tok_tiles = static_cast<int>((a.M + tok_tile - 1) / tok_tile);
   p.k_blocks = static_cast<int>((a.K + kBlockK - 1) / kBlockK);
@@ -592,27 +558,26 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
 }
 
-template <int TOK, bool kGroup, bool kMagic>
+template <int TOK, bool kGroup>
 int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
   const bool eo = a.codes_layout == SQ_CODES_EVEN_ODD;
   const bool dump = a.acc_dump != nullptr;
   const bool bf16 = a.out_dtype == SQ_BF16;
 #define SQ_LAUNCH(EO, DUMP)                                                                          \
-  (bf16 ? launch_variant<TOK, kGroup, kMagic, EO, DUMP, __nv_bfloat16>(a, tok_tile, stream)          \
-        : launch_variant<TOK, kGroup, kMagic, EO, DUMP, __half>(a, tok_tile, stream))
+  (bf16 ? launch_variant<TOK, kGroup, EO, DUMP, __nv_bfloat16>(a, tok_tile, stream)          \
+        : launch_variant<TOK, kGroup, EO, DUMP, __half>(a, tok_tile, stream))
   if (eo) return dump ? SQ_LAUNCH(true, true) : SQ_LAUNCH(true, false);
   return dump ? SQ_LAUNCH(false, true) : SQ_LAUNCH(false, false);
 #undef SQ_LAUNCH
 }
 
-template <bool kGroup, bool kMagic>
+template <bool kGroup>
 int launch_mode(const GemmArgs& a, cudaStream_t stream) {
   const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
   const int t = pick_tok_tile(a.M, ch_tiles, sm_count());
-  if (t <= 32) return launch_tok<32, kGroup, kMagic>(a, t, stream);
-  if (t <= 64) return launch_tok<64, kGroup, kMagic>(a, t, stream);
-  if (t <= 128) return launch_tok<128, kGroup, kMagic>(a, t, stream);
-  return launch_tok<160, kGroup, kMagic>(a, t, stream);
+  if (t <= 32) return launch_tok<32, kGroup>(a, t, stream);
+  if (t <= 64) return launch_tok<64, kGroup>(a, t, stream);
+  return launch_tok<128, kGroup>(a, t, stream);
 }
 
 }  // namespace
@@ -625,16 +590,16 @@ int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t st
     return SQ_ERR_ENUM;
   const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
   int t = pick_tok_tile(a.M, ch_tiles, sm_count());
-  if (t <= 128) t = 160;
-  return launch_variant<160, true, true, true, false, __nv_bfloat16, true>(a, t, stream, timeline);
+  if (t <= 64) t = 128;
+  return launch_variant<128, true, true, false, __nv_bfloat16, true>(a, t, stream, timeline);
 }
 
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   int v = validate_gemm(a);
   if (v != SQ_OK) return v;
   if (a.M == 0) return SQ_OK;
-  if (a.wscale_mode == SQ_WSCALE_GROUP_F16) return launch_mode<true, true>(a, stream);
-  return launch_mode<false, false>(a, stream);
+  if (a.wscale_mode == SQ_WSCALE_GROUP_F16) return launch_mode<true>(a, stream);
+  return launch_mode<false>(a, stream);
 }
 
 }  // namespace sq

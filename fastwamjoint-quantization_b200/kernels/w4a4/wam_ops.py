@@ -1,0 +1,55 @@
+"""W4A4 operators with the reference's names and argument order (``kernels/w4a4/wam_ops.py``).
+
+Additions that no reference call site uses: ``symmetric_dynamic_linear`` (per-token int4, optional
+rotation), the keyword ``rht_block`` (block length of the local Hadamard rotation, 128 by default) and
+float16 ``[N, K/128]`` group scales."""
+from __future__ import annotations
+
+import torch
+
+from .._common import GROUP, check_common, dynamic_linear, scheduled_linear, stream_span
+from .loader import load_extension  # noqa: F401
+
+
+def _common(x, packed, scales, bias, inverse):
+    return check_common("W4A4", 256, x, packed, scales, bias, inverse)
+
+
+def _check_signs(x, signs):
+    if signs.shape != (x.shape[-1],) or signs.device != x.device or signs.dtype != torch.float32:
+        raise ValueError("Rotation signs must be CUDA float32 [K].")
+    return signs.contiguous()
+
+
+def symmetric_scheduled_stream_linear(x, packed, scales, bias, inverse, activation_scales, gains, token_counts, call):
+    """``wam_ops.py:27-45``."""
+    x = _common(x, packed, scales, bias, inverse)
+    span = stream_span(x, gains, token_counts, activation_scales, strict_positive=True)
+    return scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, abits=4)
+
+
+def symmetric_scheduled_stream_rht_linear(x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
+                                          call, signs, *, rht_block: int = GROUP):
+    """Rotate, scale, quantize to int4, multiply (``wam_ops.py:56-75``).  The rotation is the block-local
+    power-of-two Hadamard transform of length ``rht_block``."""
+    x = _common(x, packed, scales, bias, inverse)
+    span = stream_span(x, gains, token_counts, activation_scales, strict_positive=True)
+    return scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, abits=4,
+                            signs=_check_signs(x, signs), rht_block=rht_block)
+
+
+def symmetric_dynamic_linear(x, packed, scales, bias, inverse, signs=None, *, rht_block: int = GROUP):
+    """Per-token dynamic int4 activations (device kernels ``w4a4.cu:918-961`` have no reference wrapper)."""
+    x = _common(x, packed, scales, bias, inverse)
+    return dynamic_linear(x, packed, scales, bias, inverse, abits=4,
+                          signs=None if signs is None else _check_signs(x, signs), rht_block=rht_block)
+
+
+def symmetric_scheduled_stream_adaln_linear(x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
+                                            call, adaln_scale, adaln_shift, epsilon):
+    raise NotImplementedError("The AdaLN block fusion (wam_ops.py:78-96) is not built yet; call the unfused linear.")
+
+
+def symmetric_scheduled_stream_gate_residual_linear(x, packed, scales, bias, inverse, activation_scales, gains,
+                                                    token_counts, call, residual, gate):
+    raise NotImplementedError("The gate/residual block fusion (wam_ops.py:99-118) is not built yet; call the unfused linear.")

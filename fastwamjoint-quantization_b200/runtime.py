@@ -1,0 +1,243 @@
+"""``WAMQuantLinear``: the reference's quantized Linear (``runtime.py:15-276``) on the B200 kernels.
+
+Same constructor, buffers, backend strings and errors as the reference, so code written against
+``fastwam_steerquant.runtime`` keeps working:
+
+* ``backend="reference"`` is the fake-quant forward in plain torch (``runtime.py:155-175``); it runs on
+  any device and is what the native path is compared with.
+* ``backend="cutlass_w4a8"`` / ``"cutlass_w4a4"`` keep their names (they are part of checkpoints and
+  call sites) but dispatch to the hand-written sm_100a kernels; nothing here is CUTLASS.
+
+Native buffers follow the deployment conventions (``runtime.py:88-92``, ``deployment.py:89-91``):
+``weight`` packed uint8 [N, K/2], ``weight_scales`` fp32 [N], ``input_scale`` = 1/D, ``clipping_ranges`` =
+clip / qmax, ``gamma_gains`` [calls, streams], optional ``input_rotation_signs`` fp32 [K].
+
+Rotated sites: the reference's production rotation for K = 3072 / 14336 is a full-width composite
+transform; the kernels here implement the block-local power-of-two rotation (``rotation_block``, the
+largest power of two dividing K capped at 256, or whatever the caller sets).  Both backends of this
+class use the same block, so they agree with each other.
+"""
+from __future__ import annotations
+
+from typing import Literal
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .checkpoint import QuantizedSite
+from .quant import symmetric_fake_quant
+from .rht import randomized_block_hadamard_transform, rht_block_size
+from .state import DenoiseCallState
+from .streams import FastWAMStreamConfig, expand_stream_gains, resolve_stream_layout
+from .topology import LinearSite, resolve_site_module, resolve_site_parent, stream_kind_of
+
+BACKENDS = ("reference", "cutlass_w4a8", "cutlass_w4a4")
+_BUFFERS = ("weight", "weight_scales", "input_scale", "gamma_gains", "clipping_ranges", "bias", "input_rotation_signs")
+
+
+def default_rotation_block(width: int) -> int:
+    return min(rht_block_size(width), 256)
+
+
+def _native_ops(activation_bits: int):
+    if activation_bits == 4:
+        from .kernels.w4a4 import wam_ops as ops
+    else:
+        from .kernels.w4a8 import ops
+    return ops
+
+
+class WAMQuantLinear(nn.Module):
+    """Reference or native W4A8 / W4A4 Linear with static D and per-stream gains."""
+
+    @classmethod
+    def from_packed(cls, spec: dict, tensors: dict, *, state: DenoiseCallState, stream_config: FastWAMStreamConfig,
+                    activation_bits: int):
+        """Build a native Linear straight from deployment buffers, no floating-point weight involved
+        (``runtime.py:18-47``)."""
+        if activation_bits not in (4, 8):
+            raise ValueError("Deployment supports W4A4 or W4A8.")
+        rotation = spec["rotation"]
+        if rotation not in ("none", "rht") or (rotation != "none" and activation_bits != 4):
+            raise ValueError("RHT deployment requires W4A4.")
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        self.backend = f"cutlass_w4a{activation_bits}"
+        self._native_ops = _native_ops(activation_bits)
+        self.state, self.stream_config = state, stream_config
+        self.weight_bits, self.activation_bits = 4, activation_bits
+        self.rotation = rotation
+        self.stream_names = tuple(spec["stream_names"])
+        self.supports_fused_adaln = False
+        self.supports_fused_gate_residual = False
+        for name in _BUFFERS:
+            self.register_buffer(name, tensors.get(name))
+        self.rotation_block = int(spec.get("rotation_block", default_rotation_block(self.weight.shape[1] * 2)))
+        self.site = LinearSite(spec["site_index"], spec["expert"], -1, spec["operation"], spec["module_name"], None,
+                               stream_kind_of(spec["operation"]))
+        return self
+
+    def __init__(self, source: nn.Linear, entry: QuantizedSite, *, state: DenoiseCallState,
+                 stream_config: FastWAMStreamConfig, weight_bits: int, activation_bits: int,
+                 backend: Literal["reference", "cutlass_w4a8", "cutlass_w4a4"] = "reference",
+                 fuse_block: bool = False, rotation_block: int | None = None) -> None:
+        super().__init__()
+        entry.validate(state.num_calls)
+        if backend not in BACKENDS:
+            raise ValueError(f"Unsupported WAM backend: {backend}.")
+        native = backend != "reference"
+        if native and (weight_bits != 4 or activation_bits != (4 if backend == "cutlass_w4a4" else 8)):
+            raise ValueError(f"WAM {backend} does not match W{weight_bits}A{activation_bits}.")
+        rotated = entry.rotation != "none"
+        if rotated and backend == "cutlass_w4a8":
+            raise ValueError("Rotated WAM requires reference or cutlass_w4a4.")
+        if rotated and fuse_block:
+            raise ValueError("Rotated FastWAM block fusion is not validated; leave fuse_block=False.")
+        device = source.weight.device
+        qmax = (1 << (activation_bits - 1)) - 1
+        self.rotation = entry.rotation
+        self.rotation_block = int(rotation_block or default_rotation_block(entry.qweight.shape[1]))
+        signs = entry.input_rotation_signs
+        self.register_buffer("input_rotation_signs", None if signs is None else signs.float().to(device))
+        if native:
+            ops = _native_ops(activation_bits)
+            self._native_ops = ops
+            from .kernels.w4a8 import pack_signed_int4
+            self.register_buffer("weight", pack_signed_int4(entry.qweight).to(device))
+            self.register_buffer("weight_scales", entry.weight_scales.float().reshape(-1).to(device))
+            self.register_buffer("input_scale", entry.input_scale.float().reciprocal().to(device))
+            self.register_buffer("gamma_gains", entry.gamma_gains.float().to(device))
+            self.register_buffer("clipping_ranges", (entry.clipping_ranges.float() / qmax).to(device))
+        else:
+            dtype = source.weight.dtype
+            # dequantize once at load instead of at every call (runtime.py:94-98)
+            self.register_buffer("weight", entry.qweight.to(device=device, dtype=dtype)
+                                 * entry.weight_scales.to(device=device, dtype=dtype))
+            self.register_buffer("weight_scales", None)
+            self.register_buffer("input_scale", entry.input_scale.clone())
+            self.register_buffer("gamma_gains", entry.gamma_gains.clone())
+            self.register_buffer("clipping_ranges", entry.clipping_ranges.clone())
+        self.register_buffer("bias", None if source.bias is None else source.bias.detach().clone())
+        self.state, self.stream_config = state, stream_config
+        self.weight_bits, self.activation_bits = int(weight_bits), int(activation_bits)
+        self.backend = backend
+        self.stream_names = entry.stream_names
+        self.supports_fused_adaln = bool(fuse_block and native and entry.operation == "ffn.0")
+        self.supports_fused_gate_residual = bool(fuse_block and native and entry.operation in {"self_attn.o", "ffn.2"})
+        # the replaced bf16 Linear is deliberately not kept (it would stay resident on the GPU)
+        self.site = LinearSite(entry.site_index, entry.expert, -1, entry.operation, entry.module_name, None,
+                               stream_kind_of(entry.operation))
+
+    @property
+    def in_features(self) -> int:
+        return self.weight.shape[1] * (1 if self.backend == "reference" else 2)
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
+    def _layout(self, x: torch.Tensor, what: str):
+        layout = resolve_stream_layout(self.site, x.shape[-2], self.stream_config)
+        if self.backend != "reference" and layout.names != self.stream_names:
+            raise RuntimeError(f"WAM {what} stream names differ from {self.site.module_name}: {layout.names}.")
+        return layout
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        call = self.state.require()
+        layout = self._layout(x, "checkpoint")
+        if self.backend != "reference":
+            args = (x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges,
+                    self.gamma_gains, layout.token_counts, call)
+            if self.input_rotation_signs is not None:
+                return self._native_ops.symmetric_scheduled_stream_rht_linear(
+                    *args, self.input_rotation_signs, rht_block=self.rotation_block)
+            return self._native_ops.symmetric_scheduled_stream_linear(*args)
+        return self._reference_forward(x, call, layout)
+
+    def _reference_forward(self, x, call, layout):
+        """Fake-quant forward of the reference (``runtime.py:155-175``), dividing order."""
+        if self.input_rotation_signs is not None:
+            x = randomized_block_hadamard_transform(x.float(), self.input_rotation_signs, self.rotation_block).to(x.dtype)
+        gains = self.gamma_gains[call].to(device=x.device, dtype=torch.float32)
+        if gains.numel() != layout.num_streams:
+            raise RuntimeError(f"Runtime stream count changed for {self.site.module_name}: "
+                               f"checkpoint={gains.numel()}, input={layout.num_streams}.")
+        scaled = x.float() / self.input_scale.to(x.device)[None, :]
+        row_gain = expand_stream_gains(scaled, gains, layout)
+        step = self.clipping_ranges[call].to(x.device) / ((1 << (self.activation_bits - 1)) - 1)
+        qx = (symmetric_fake_quant(scaled * row_gain, bits=self.activation_bits, scale=step) / row_gain).to(x.dtype)
+        bias = None if self.bias is None else self.bias.to(device=x.device, dtype=x.dtype)
+        return F.linear(qx, self.weight, bias)
+
+    def forward_adaln(self, x, scale, shift, epsilon: float):
+        if not self.supports_fused_adaln:
+            raise RuntimeError("WAM AdaLN block fusion was not enabled for this site.")
+        layout = self._layout(x, "fused AdaLN")
+        return self._native_ops.symmetric_scheduled_stream_adaln_linear(
+            x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
+            layout.token_counts, self.state.require(), scale, shift, epsilon)
+
+    def forward_gate_residual(self, x, residual, gate):
+        if not self.supports_fused_gate_residual:
+            raise RuntimeError("WAM gate/residual block fusion was not enabled for this site.")
+        layout = self._layout(x, "fused residual")
+        return self._native_ops.symmetric_scheduled_stream_gate_residual_linear(
+            x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
+            layout.token_counts, self.state.require(), residual, gate)
+
+
+def set_wam_block_fusions(model: nn.Module, enabled: bool) -> int:
+    """Toggle the three fusable operations per expert block (``runtime.py:208-223``)."""
+    if getattr(model, "_rollout_graph", None) is not None:
+        raise RuntimeError("Cannot change block fusion after CUDA Graph installation.")
+    modules = [m for m in model.modules() if isinstance(m, WAMQuantLinear)]
+    if enabled and any(m.rotation != "none" for m in modules):
+        raise ValueError("Rotated FastWAM block fusion is not validated.")
+    count = 0
+    for module in modules:
+        if module.backend == "reference":
+            continue
+        module.supports_fused_adaln = bool(enabled and module.site.operation == "ffn.0")
+        module.supports_fused_gate_residual = bool(enabled and module.site.operation in {"self_attn.o", "ffn.2"})
+        count += int(module.supports_fused_adaln or module.supports_fused_gate_residual)
+    return count
+
+
+def apply_checkpoint(model: nn.Module, checkpoint, *, state: DenoiseCallState | None = None,
+                     backend: Literal["reference", "cutlass_w4a8", "cutlass_w4a4"] = "reference",
+                     fuse_block: bool = False):
+    """Replace every site's ``nn.Linear`` by a ``WAMQuantLinear`` (``runtime.py:226-276``).  ``checkpoint``
+    needs ``validate()``, ``sites``, ``weight_bits``, ``activation_bits``, ``num_calls`` and
+    ``stream_config`` like the reference's ``QuantizationCheckpoint``.  All sites are validated before the
+    first replacement; replacement is one site at a time so no second copy of the model exists."""
+    checkpoint.validate()
+    rotated = any(site.rotation != "none" for site in checkpoint.sites)
+    if rotated and (fuse_block or backend == "cutlass_w4a8"):
+        raise ValueError("Rotated WAM requires W4A4/reference with block fusion disabled.")
+    if backend not in BACKENDS:
+        raise ValueError(f"Unsupported WAM backend: {backend}.")
+    if backend != "reference" and (checkpoint.weight_bits != 4 or backend != f"cutlass_w4a{checkpoint.activation_bits}"):
+        raise ValueError("WAM native backend and checkpoint bit widths must match.")
+    state = DenoiseCallState(checkpoint.num_calls) if state is None else state
+    if state.num_calls != checkpoint.num_calls:
+        raise ValueError("Runtime call state and checkpoint call counts differ.")
+    stream_config = FastWAMStreamConfig(**checkpoint.stream_config)
+    alignment = 256 if backend == "cutlass_w4a4" else 32
+    for entry in checkpoint.sites:
+        module = resolve_site_module(model, entry.module_name)
+        if not isinstance(module, nn.Linear):
+            raise TypeError(f"{entry.module_name} is not an nn.Linear.")
+        if module.weight.shape != entry.qweight.shape:
+            raise ValueError(f"WAM checkpoint shape differs from {entry.module_name}.")
+        if backend != "reference" and (module.in_features % alignment or module.out_features % 8):
+            raise ValueError(f"Unsupported {backend} shape at {entry.module_name}.")
+    for entry in checkpoint.sites:
+        module = resolve_site_module(model, entry.module_name)
+        parent, child = resolve_site_parent(model, entry.module_name)
+        replacement = WAMQuantLinear(module, entry, state=state, stream_config=stream_config,
+                                     weight_bits=checkpoint.weight_bits, activation_bits=checkpoint.activation_bits,
+                                     backend=backend, fuse_block=fuse_block).to(module.weight.device)
+        replacement.train(module.training)
+        setattr(parent, child, replacement)
+    return state, len(checkpoint.sites)
