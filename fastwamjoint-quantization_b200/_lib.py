@@ -14,6 +14,8 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libsq_b200.so"
 
 # status codes of include/sq_b200.h
 OK, ERR_NULL, ERR_SHAPE, ERR_ENUM, ERR_INDEX, ERR_DRIVER, ERR_WORKSPACE, ERR_DEVICE_WAIT = 0, -1, -2, -3, -4, -5, -6, -7
+ERR_SCRATCH_LIMIT = -8
+NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024 + 65536
 BF16, FP16 = 0, 1
 ACT_STATIC, ACT_TOKEN = 0, 1
 CODES_NATURAL, CODES_EVEN_ODD = 0, 1
@@ -32,6 +34,9 @@ _SIGNATURES = {
     "sq_linear": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "sq_linear_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
+                                  c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                  c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "sq_device_status": (c_int, []),
     "sq_status_string": (c_char_p, [c_int]),
     "sq_version": (c_char_p, []),

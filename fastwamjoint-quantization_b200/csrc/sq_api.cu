@@ -121,6 +121,31 @@ int launch_gemm_check(const GemmArgs& a, cudaStream_t stream) {
 
 static size_t round256(size_t v) { return (v + 255u) & ~static_cast<size_t>(255u); }
 
+// ------------------------------------------------------------------ library-owned scratch (sq_linear_noalloc)
+// Scratch for callers that cannot allocate: a fixed array in the library's own device image.  Every GPU that
+// loads the library carries it until the process exits.  In host code the name below is only a handle for
+// the runtime, not a device address; the address is looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SQ_NOALLOC_SCRATCH_BYTES];
+
+// Device address of the scratch array on the current device (looked up on first use), or null with *err set.
+static void* noalloc_scratch_ptr(cudaError_t* err) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= 64) {
+    *err = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    *err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (*err != cudaSuccess) return nullptr;
+    cached[dev] = ptr;
+  }
+  return cached[dev];
+}
+
 }  // namespace sq
 
 // ====================================================================== C ABI
@@ -214,6 +239,22 @@ int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, in
   return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
 }
 
+int sq_linear_noalloc(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+                      const float* inv_d, const float* signs, int rht_block, const float* act_scales,
+                      const float* gains, int64_t calls, int64_t call, int64_t span, int64_t streams,
+                      int64_t seq_tokens, const void* w_packed, const void* w_scales, int wscale_mode,
+                      const void* bias, void* out, void* stream) {
+  if (rows < 0 || K <= 0) return SQ_ERR_SHAPE;
+  const size_t need = sq_workspace_bytes(rows, K);
+  if (need > static_cast<size_t>(SQ_NOALLOC_SCRATCH_BYTES)) return SQ_ERR_SCRATCH_LIMIT;
+  cudaError_t err = cudaSuccess;
+  void* scratch = sq::noalloc_scratch_ptr(&err);
+  if (scratch == nullptr) return err != cudaSuccess ? static_cast<int>(err) : SQ_ERR_DRIVER;
+  // Nothing in the scratch has to start at zero: the pre-pass writes every code and row scale the GEMM reads.
+  return sq_linear(x, x_dtype, rows, K, N, abits, mode, inv_d, signs, rht_block, act_scales, gains, calls, call, span,
+                   streams, seq_tokens, w_packed, w_scales, wscale_mode, bias, out, scratch, need, stream);
+}
+
 int sq_device_status(void) {
   int* word = sq::device_status_word();
   if (word == nullptr) return SQ_ERR_DRIVER;
@@ -237,6 +278,7 @@ const char* sq_status_string(int status) {
     case SQ_ERR_DRIVER: return "CUDA driver call failed";
     case SQ_ERR_WORKSPACE: return "workspace too small";
     case SQ_ERR_DEVICE_WAIT: return "a kernel gave up a bounded wait";
+    case SQ_ERR_SCRATCH_LIMIT: return "rows * K is beyond the library-owned scratch of sq_linear_noalloc";
     case 9001: return "device: TMA producer timed out waiting for a free stage";
     case 9002: return "device: MMA warp timed out waiting for a free accumulator";
     case 9003: return "device: MMA warp timed out waiting for operands";

@@ -31,6 +31,7 @@ extern "C" {
 #define SQ_ERR_DRIVER (-5)    /* the CUDA driver refused a tensor-map encode           */
 #define SQ_ERR_WORKSPACE (-6) /* workspace smaller than sq_workspace_bytes()           */
 #define SQ_ERR_DEVICE_WAIT (-7) /* a kernel gave up a bounded wait (see sq_device_status) */
+#define SQ_ERR_SCRATCH_LIMIT (-8) /* sq_linear_noalloc: the linear needs more scratch than the library owns */
 
 /* element types of activations / outputs */
 #define SQ_BF16 0
@@ -127,6 +128,33 @@ int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, in
               int64_t span, int64_t streams, int64_t seq_tokens,
               const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
               void* out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* sq_linear for callers that cannot allocate device memory.  It has no counterpart in the reference, whose
+ * operators always allocate their scratch per call (torch::empty, w4a8.cu:1358-1360).
+ *
+ * Who needs it: code that runs after a point where allocation is off the table - a control loop that must
+ * not hit the implicit device synchronisation of cudaMalloc, a host framework whose own pool already holds
+ * all free device memory (so cudaMalloc would simply fail), or a plug-in that is handed device pointers but
+ * no allocator.  Such a caller still passes its input, weights and output; the codes and row scales that
+ * live between the pre-pass and the GEMM go into an array of SQ_NOALLOC_SCRATCH_BYTES that is part of the
+ * library image on every GPU that loads it.  This function calls no cudaMalloc, cudaFree or other
+ * allocating routine.
+ *
+ * Limit: sq_workspace_bytes(rows, K) <= SQ_NOALLOC_SCRATCH_BYTES, i.e. about rows * K <= 8 Mi elements
+ * (2048 x 3072 fits, 4096 x 3072 does not); larger calls return SQ_ERR_SCRATCH_LIMIT and launch nothing.
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress, with that device current);
+ * make that first call outside any stream capture.
+ * All calls on a device share the one array and it keeps the previous call's contents.  Nothing in it needs
+ * clearing (each call overwrites what it reads), but two calls that overlap on the GPU - different streams
+ * without an ordering between them - race on it; order them.
+ * Arguments and results are those of sq_linear without `workspace` / `workspace_bytes`. */
+#define SQ_NOALLOC_SCRATCH_BYTES (8u * 1024u * 1024u + 65536u)
+int sq_linear_noalloc(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+                      const float* inv_d, const float* signs, int rht_block,
+                      const float* act_scales, const float* gains, int64_t calls, int64_t call,
+                      int64_t span, int64_t streams, int64_t seq_tokens,
+                      const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
+                      void* out, void* stream);
 
 /* Reads (and clears) the device-side status word of the current device.  Kernels never spin forever:
  * a wait that exceeds its time limit records a code here and the kernel returns.  0 = no kernel gave up.
