@@ -1,0 +1,158 @@
+"""Synthetic DiT stack of the benchmark configurations: 30 blocks, hidden 3072, 24 heads of 128, QKV
+3072->9216, attention out 3072->3072, FFN 3072->12288 (GELU) ->3072, RMSNorm, residuals; batch 1 with 1560
+latent + 32 action tokens.  Every linear is a ``TokenQuantLinear`` (int4 weights with fp16 group-128 scales,
+per-token int8 or int4 activations, optional block-local 128-point rotation); attention stays in bf16
+(``scaled_dot_product_attention``).  The reference's model (FastWAMJoint) is not available, so the weights are
+random (N(0, 0.02), per-layer seeds) and the stack exists to measure and check one captured denoising step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import native
+from .kernels.w4a8.ops import pack_signed_int4
+from .quant import GROUP, quantize_weight_group
+from .rht import randomized_block_hadamard_transform, rht_signs, rotate_weight_
+
+
+class TokenQuantLinear(nn.Module):
+    """Group-128 W4 linear with per-token dynamic activations.
+
+    ``backend="native"`` runs the B200 kernels; ``backend="reference"`` is the fake-quant restatement in plain
+    torch (rotate -> round to the model dtype -> per-token fake-quant -> ``F.linear`` against the dequantized
+    weight), the form the reference's CPU module has (``runtime.py:155-175``).  Both read the same buffers, so
+    switching ``backend`` compares like with like."""
+
+    def __init__(self, weight: torch.Tensor, *, activation_bits: int, rotate: bool, module_name: str,
+                 bias: torch.Tensor | None = None, backend: str = "native", rotation_seed: int = 0):
+        super().__init__()
+        n, k = weight.shape
+        signs = None
+        if rotate:
+            signs = rht_signs(k, seed=rotation_seed, module_name=module_name, device=weight.device)
+            weight = rotate_weight_(weight.clone(), signs)
+        codes, scales = quantize_weight_group(weight.float())
+        self.register_buffer("weight", pack_signed_int4(codes.cpu()).to(weight.device))
+        self.register_buffer("weight_scales", scales.contiguous())
+        self.register_buffer("bias", bias)
+        self.register_buffer("input_rotation_signs", signs)
+        self.activation_bits, self.backend = int(activation_bits), backend
+        self.in_features, self.out_features = k, n
+        self._dequantized: torch.Tensor | None = None
+        self.workspace: torch.Tensor | None = None  # shared scratch set by the owning stack
+
+    def _reference_weight(self, dtype):
+        if self._dequantized is None or self._dequantized.dtype != dtype:
+            low = (self.weight & 0x0F).to(torch.int16)
+            high = (self.weight >> 4).to(torch.int16)
+            both = torch.stack((low, high), dim=-1).reshape(self.out_features, self.in_features)
+            codes = torch.where(both >= 8, both - 16, both).float()
+            scales = self.weight_scales.float().repeat_interleave(GROUP, dim=1)
+            self._dequantized = (codes * scales).to(dtype)
+        return self._dequantized
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.backend == "native":
+            return native.linear(x, self.weight, self.weight_scales, self.bias, abits=self.activation_bits,
+                                 mode="token", signs=self.input_rotation_signs, workspace=self.workspace)
+        values = x.float()
+        if self.input_rotation_signs is not None:
+            values = randomized_block_hadamard_transform(values, self.input_rotation_signs, 128).to(x.dtype).float()
+        qmax = (1 << (self.activation_bits - 1)) - 1
+        amax = values.abs().amax(dim=-1, keepdim=True)
+        # tensor / tensor: on CUDA, torch turns division by a Python scalar into a multiply by its reciprocal,
+        # which moves the scale by one ulp and flips int4 codes at rounding ties
+        scale = (amax / torch.full_like(amax, float(qmax))).clamp_min(1e-8)
+        qx = ((values / scale).round().clamp(-qmax, qmax) * scale).to(x.dtype)
+        return F.linear(qx, self._reference_weight(x.dtype), self.bias)
+
+
+@dataclass(frozen=True)
+class DiTConfig:
+    blocks: int = 30
+    hidden: int = 3072
+    heads: int = 24
+    ffn: int = 12288
+    activation_bits: int = 8
+    rotate: bool = False
+    latent_tokens: int = 1560
+    action_tokens: int = 32
+    eps: float = 1e-6
+
+    @property
+    def tokens(self) -> int:
+        return self.latent_tokens + self.action_tokens
+
+
+def rms_norm(x: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm with unit weight, fp32 statistics."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + eps)).to(x.dtype)
+
+
+class DiTBlock(nn.Module):
+    OPERATIONS = ("attn.qkv", "attn.o", "ffn.0", "ffn.2")
+
+    def __init__(self, config: DiTConfig, index: int, device, dtype, backend: str):
+        super().__init__()
+        self.config = config
+        h, f = config.hidden, config.ffn
+        shapes = {"attn.qkv": (3 * h, h), "attn.o": (h, h), "ffn.0": (f, h), "ffn.2": (h, f)}
+        layers = {}
+        for j, op in enumerate(self.OPERATIONS):
+            generator = torch.Generator(device=device).manual_seed(1000 + 4 * index + j)
+            weight = (torch.randn(shapes[op], generator=generator, device=device) * 0.02).to(dtype)
+            layers[op] = TokenQuantLinear(weight, activation_bits=config.activation_bits, rotate=config.rotate,
+                                          module_name=f"blocks.{index}.{op}", backend=backend)
+        self.qkv, self.o, self.up, self.down = (layers[op] for op in self.OPERATIONS)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        cfg = self.config
+        b, m, h = x.shape
+        qkv = self.qkv(rms_norm(x, cfg.eps)).reshape(b, m, 3, cfg.heads, h // cfg.heads)
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        attn = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, m, h)
+        x = x + self.o(attn)
+        return x + self.down(F.gelu(self.up(rms_norm(x, cfg.eps))))
+
+
+class SyntheticDiT(nn.Module):
+    """The stack plus the two hooks the live-graph glue wraps (``_joint_denoise_core``, ``infer_action``)."""
+
+    def __init__(self, config: DiTConfig = DiTConfig(), *, device="cuda", dtype=torch.bfloat16, backend: str = "native"):
+        super().__init__()
+        self.config = config
+        self.blocks = nn.ModuleList(DiTBlock(config, i, device, dtype, backend) for i in range(config.blocks))
+        if backend == "native":
+            biggest = max(config.hidden, config.ffn)
+            size = native._lib.load_library().sq_workspace_bytes(config.tokens, biggest)
+            self.register_buffer("workspace", torch.empty(size, dtype=torch.uint8, device=device), persistent=False)
+            for module in self.modules():
+                if isinstance(module, TokenQuantLinear):
+                    module.workspace = self.workspace
+
+    def set_backend(self, backend: str) -> None:
+        for module in self.modules():
+            if isinstance(module, TokenQuantLinear):
+                module.backend = backend
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        x = tokens
+        for block in self.blocks:
+            x = block(x)
+        return rms_norm(x, self.config.eps)
+
+    # hooks with the names LiveJointDiTGraph replaces
+    def _joint_denoise_core(self, tokens: torch.Tensor):
+        return (self.forward(tokens),)
+
+    def infer_action(self, tokens: torch.Tensor, num_inference_steps: int = 1, text_cfg_scale: float = 1.0):
+        x = tokens
+        for _ in range(num_inference_steps):
+            (velocity,) = self._joint_denoise_core(x)
+            x = x - velocity / num_inference_steps
+        return x

@@ -165,7 +165,9 @@ class WAMQuantLinear(nn.Module):
                                f"checkpoint={gains.numel()}, input={layout.num_streams}.")
         scaled = x.float() / self.input_scale.to(x.device)[None, :]
         row_gain = expand_stream_gains(scaled, gains, layout)
-        step = self.clipping_ranges[call].to(x.device) / ((1 << (self.activation_bits - 1)) - 1)
+        clip = self.clipping_ranges[call].to(x.device)
+        # tensor / tensor keeps IEEE division on CUDA too (a Python-scalar divisor becomes a reciprocal multiply)
+        step = clip / torch.full_like(clip, float((1 << (self.activation_bits - 1)) - 1))
         qx = (symmetric_fake_quant(scaled * row_gain, bits=self.activation_bits, scale=step) / row_gain).to(x.dtype)
         bias = None if self.bias is None else self.bias.to(device=x.device, dtype=x.dtype)
         return F.linear(qx, self.weight, bias)
