@@ -36,7 +36,7 @@ class TokenQuantLinear(nn.Module):
             signs = rht_signs(k, seed=rotation_seed, module_name=module_name, device=weight.device)
             weight = rotate_weight_(weight.clone(), signs)
         codes, scales = quantize_weight_group(weight.float())
-        self.register_buffer("weight", pack_signed_int4(codes.cpu()).to(weight.device))
+        self.register_buffer("weight", pack_signed_int4(codes))
         self.register_buffer("weight_scales", scales.contiguous())
         self.register_buffer("bias", bias)
         self.register_buffer("input_rotation_signs", signs)
