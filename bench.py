@@ -34,6 +34,9 @@ WORKLOADS = {
     "m16384": (16384, 3072, 3072, 4, True),
 }
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch from the committed ncu capture
+# (profiles/sq_gemm_tc_kernel_c2_w4a4_rht.md); other workloads have no capture
+NCU_TRAFFIC_BYTES = {"c2": 11.20e6}
 
 
 def algorithmic_bytes(m, k, n, rotate):
@@ -477,7 +480,7 @@ def main():
         t_hbm = algorithmic_bytes(m, k, n, rotate) / (hbm_peak * 1e9)
         if t_compute >= t_hbm:
             roofline = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s",
-                        "frac": gemm_tops / int8_peak, "traffic": None,
+                        "frac": gemm_tops / int8_peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                         "peak_source": int8_source}
         else:
             gbs = algorithmic_bytes(m, k, n, rotate) / (gemm_ms * 1e-3) / 1e9

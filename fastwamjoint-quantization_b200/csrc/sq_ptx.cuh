@@ -82,20 +82,33 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// try_wait that may stay suspended in hardware for up to `hint_ns` before it reports "not yet"; it
+// returns as soon as the phase completes, so a long hint costs no latency and saves issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+
 // Wait for `parity` of barrier `bar`.  Returns false when the wait gave up: either
 // `*abort_flag` (shared memory, set by any role that timed out) became non-zero or
 // `limit_ns` of wall-clock passed.  On a timeout the caller records the status.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t start = global_timer_ns();
-  uint32_t spins = 0;
+  const uint64_t start = global_timer_ns();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (global_timer_ns() - start > limit_ns) return false;
-    }
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;  // up to 20 us asleep per poll
+    if (*abort_flag != 0) return false;
+    if (global_timer_ns() - start > limit_ns) return false;
   }
 }
 
