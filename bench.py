@@ -159,6 +159,65 @@ def measure_int8_peak(device):
 DIT_WORKLOADS = {"dit_a8": (8, False), "dit_a4": (4, True)}
 
 
+def run_nsplit(args):
+    """Output-channel split of the widest layer (3072 -> 12288, W4A4+RHT, M = 4096 tokens on every rank): rank r
+    holds W[r*N/G:(r+1)*N/G], computes [M, N/G] and the slices are all-gathered with NCCL over NVLink.  The
+    gather moves 2*M*N*(G-1)/G bytes per rank and dominates the step; reported as measured."""
+    import torch.distributed as dist
+    rank, local_rank, world = (int(os.environ.get(k, d)) for k, d in (("RANK", "0"), ("LOCAL_RANK", "0"), ("WORLD_SIZE", "1")))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no multi-GPU path; use --workload m4096_ffn_up"}), flush=True)
+        return
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    else:
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29531", rank=0, world_size=1, device_id=device)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from fastwamjoint_quantization_b200 import native, sharding
+    oracle = load_oracle()
+    m, k, n = 4096, 3072, 12288
+    case = oracle.prepare_token_linear(m, k, n, abits=4, seed=0)
+    c0, c1 = sharding.channel_range(n, rank, world)
+    packed = oracle.pack_signed_int4(case["qweight"][c0:c1].contiguous()).to(device)
+    scales = case["weight_scales"][c0:c1].contiguous().to(device)
+    x, signs = case["x"].to(device), case["signs"].to(device)
+    step = lambda: sharding.channel_split_linear(x, lambda t: native.linear(t, packed, scales, None, abits=4, mode="token", signs=signs))
+    out = step()
+    want = oracle.linear_token(case["x"][:32], case["qweight"], case["weight_scales"], None, abits=4, signs=case["signs"],
+                               want_accumulators=False)["out"]
+    err = ((out[:32].cpu().float() - want.float()).norm() / want.float().norm()).item()
+    if not err < 1e-2:
+        raise SystemExit(f"gathered output differs from the oracle: {err}")
+    for _ in range(max(args.warmup, 3)):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "W4A4+RHT GEMM int-TOPS", "value": 2.0 * m * n * k / (ms * 1e-3) / 1e12, "unit": "TOPS",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4 -> int32",
+            "data": "synthetic",
+            "config": {"workload": "nsplit_ffn_up", "M": m, "K": k, "N": n, "split": "output channels across ranks + NCCL all-gather",
+                       "gather_bytes_per_rank": 2 * m * n * (world - 1) // world},
+            "gpu_launches": 2 * args.steps, "parity_rel_fro": err}), flush=True)
+    dist.destroy_process_group()
+
+
 def run_dit(args):
     """30-block synthetic DiT step (BASELINE.json configs 3 / 4): hidden 3072, 24 heads, FFN 12288, 1592 tokens,
     every linear quantized, one denoising step captured and replayed as one CUDA graph.  Reports ms per step
@@ -304,10 +363,15 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
-    parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(DIT_WORKLOADS))
+    parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(DIT_WORKLOADS) + ["nsplit_ffn_up"])
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
+    if args.workload == "nsplit_ffn_up":
+        if args.steps == 200:
+            args.steps = 50
+        run_nsplit(args)
+        return
     if args.workload in DIT_WORKLOADS:
         if args.steps == 200:
             args.steps = 20
