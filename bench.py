@@ -495,24 +495,52 @@ def main():
     timed_replay(prepass_graph)
     prepass_ms = timed_replay(prepass_graph) / args.steps
 
-    # end to end through the public call with HOST buffers: pinned x -> device, linear, result -> pinned host
-    x_host = case["x"].pin_memory()
-    out_host = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
-    x_dev = torch.empty_like(xs[0])
-    e2e_steps = max(5, min(args.steps, 50))
-    for i in range(3):
-        x_dev.copy_(x_host, non_blocking=True)
-        out_host.copy_(native.linear(x_dev, packs[0], wss[0], bias, abits=abits, mode="token", signs=signs), non_blocking=True)
+    # End to end through the public call with HOST buffers: every step copies its input from pinned host memory
+    # and its result back to pinned host memory.  Copies and compute of consecutive steps overlap on three
+    # streams with two device buffers each way (the copy engines are independent of the SMs); every byte of
+    # every step still crosses PCIe inside the timed region.
+    depth = 2
+    x_host = [case["x"].pin_memory() for _ in range(depth)]
+    out_host = [torch.empty((m, n), dtype=torch.bfloat16).pin_memory() for _ in range(depth)]
+    x_dev = [torch.empty_like(xs[0]) for _ in range(depth)]
+    out_dev = [torch.empty((m, n), device=device, dtype=torch.bfloat16) for _ in range(depth)]
+    ws_dev = [torch.empty((lib_ws,), device=device, dtype=torch.uint8) for _ in range(depth)]
+    copy_in, copy_out, main = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    in_done = [torch.cuda.Event() for _ in range(depth)]
+    run_done = [torch.cuda.Event() for _ in range(depth)]
+    out_done = [torch.cuda.Event() for _ in range(depth)]
+
+    def e2e_loop(count):
+        for i in range(count):
+            b, j = i % depth, i % nsets
+            with torch.cuda.stream(copy_in):
+                copy_in.wait_event(run_done[b])  # the previous use of this input buffer has been consumed
+                x_dev[b].copy_(x_host[b], non_blocking=True)
+                in_done[b].record()
+            main.wait_event(in_done[b])
+            main.wait_event(out_done[b])  # the previous result in this output buffer has left the device
+            native.linear(x_dev[b], packs[j], wss[j], bias, abits=abits, mode="token", signs=signs, out=out_dev[b],
+                          workspace=ws_dev[b])
+            run_done[b].record()
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(run_done[b])
+                out_host[b].copy_(out_dev[b], non_blocking=True)
+                out_done[b].record()
+        main.wait_stream(copy_in)
+        main.wait_stream(copy_out)
+
+    e2e_steps = max(5, min(args.steps, 100))
+    e2e_loop(4)
     barrier()
     h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     h0.record()
-    for i in range(e2e_steps):
-        j = i % nsets
-        x_dev.copy_(x_host, non_blocking=True)
-        out_host.copy_(native.linear(x_dev, packs[j], wss[j], bias, abits=abits, mode="token", signs=signs), non_blocking=True)
+    e2e_loop(e2e_steps)
     h1.record()
     barrier()
     e2e_ms = h0.elapsed_time(h1)
+    e2e_err = ((out_host[0][:rows].float() - want.float()).norm() / want.float().norm()).item()
+    if not e2e_err < 1e-2:
+        raise SystemExit(f"end-to-end output differs from the oracle: relative Frobenius error {e2e_err}")
     clocks = sampler.stop()
     status = native.device_status()
     if status != 0:
@@ -565,8 +593,9 @@ def main():
                        "l2": "rotating %d input sets (%.0f MB > 126 MB L2)" % (nsets, nsets * set_bytes / 1e6),
                        "launch": "the K steps are replayed as one CUDA graph"},
             "gpu_launches": 2 * args.steps,
-            "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": x_host.numel() * 2,
-                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": e2e_ms / e2e_steps},
+            "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": x_host[0].numel() * 2,
+                    "d2h_bytes_per_step": out_host[0].numel() * 2, "ms_per_step": e2e_ms / e2e_steps,
+                    "pipeline": "host->device copy, linear and device->host copy of consecutive steps overlap (3 streams, 2 buffers)"},
             "roofline": roofline, "clocks": clocks, "parity_rel_fro": err,
         }
         if not args.no_cpu_baseline:
