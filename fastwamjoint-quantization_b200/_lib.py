@@ -6,7 +6,7 @@ present when a kernel is requested, the call raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 from functools import lru_cache
 from pathlib import Path
 
@@ -20,6 +20,8 @@ BF16, FP16 = 0, 1
 ACT_STATIC, ACT_TOKEN = 0, 1
 CODES_NATURAL, CODES_EVEN_ODD = 0, 1
 WSCALE_CHANNEL_F32, WSCALE_GROUP_F16 = 0, 1
+NORM_NONE, NORM_LAYER, NORM_RMS = 0, 1, 2
+ACT_FN_NONE, ACT_FN_GELU = 0, 1
 
 _SIGNATURES = {
     "sq_prepass": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -34,6 +36,12 @@ _SIGNATURES = {
     "sq_linear": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "sq_linear_fused": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
+                                c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                c_void_p, c_void_p, c_int, c_void_p,
+                                c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
+                                c_int, c_void_p, c_int64, c_int64, c_void_p,
+                                c_void_p, c_void_p, c_size_t, c_void_p]),
     "sq_linear_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),

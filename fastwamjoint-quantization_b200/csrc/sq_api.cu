@@ -35,6 +35,8 @@ int validate_gemm(const GemmArgs& a) {
   if (a.codes_layout != SQ_CODES_NATURAL && a.codes_layout != SQ_CODES_EVEN_ODD) return SQ_ERR_ENUM;
   if (a.wscale_mode != SQ_WSCALE_CHANNEL_F32 && a.wscale_mode != SQ_WSCALE_GROUP_F16) return SQ_ERR_ENUM;
   if (a.out_dtype != SQ_BF16 && a.out_dtype != SQ_FP16) return SQ_ERR_ENUM;
+  if (a.activation != SQ_ACT_FN_NONE) return SQ_ERR_ENUM;  // activations are fused on the input side only
+  if (a.gate != nullptr && (a.gate_span <= 0 || a.gate_row_stride < a.N)) return SQ_ERR_SHAPE;
   if (a.M < 0 || a.N <= 0 || a.K <= 0) return SQ_ERR_SHAPE;
   if (a.K % 32 != 0 || a.N % 8 != 0 || a.K < 128) return SQ_ERR_SHAPE;
   if (a.wscale_mode == SQ_WSCALE_GROUP_F16 && a.K % 128 != 0) return SQ_ERR_SHAPE;
@@ -175,6 +177,8 @@ static sq::GemmArgs make_args(const void* codes, int codes_layout, const void* w
   a.out_dtype = out_dtype;
   a.M = M; a.N = N; a.K = K;
   a.acc_dump = acc_dump;
+  a.activation = SQ_ACT_FN_NONE;
+  a.gate = nullptr; a.gate_span = 1; a.gate_row_stride = 0; a.residual = nullptr;
   return a;
 }
 
@@ -211,6 +215,21 @@ int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, in
               int64_t call, int64_t span, int64_t streams, int64_t seq_tokens, const void* w_packed,
               const void* w_scales, int wscale_mode, const void* bias, void* out, void* workspace,
               size_t workspace_bytes, void* stream) {
+  return sq_linear_fused(x, x_dtype, rows, K, N, abits, mode, inv_d, signs, rht_block, act_scales, gains, calls, call,
+                         span, streams, seq_tokens, w_packed, w_scales, wscale_mode, bias, SQ_ACT_FN_NONE, SQ_NORM_NONE, 0.0f,
+                         nullptr, nullptr, nullptr, 1, 0, 0, SQ_ACT_FN_NONE, nullptr, 1, 0, nullptr, out, workspace,
+                         workspace_bytes, stream);
+}
+
+int sq_linear_fused(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+                    const float* inv_d, const float* signs, int rht_block, const float* act_scales,
+                    const float* gains, int64_t calls, int64_t call, int64_t span, int64_t streams,
+                    int64_t seq_tokens, const void* w_packed, const void* w_scales, int wscale_mode,
+                    const void* bias, int input_activation, int norm_kind, float norm_eps, const void* norm_weight,
+                    const void* mod_scale,
+                    const void* mod_shift, int64_t mod_span, int64_t mod_row_stride, int round_after_norm,
+                    int activation, const void* gate, int64_t gate_span, int64_t gate_row_stride,
+                    const void* residual, void* out, void* workspace, size_t workspace_bytes, void* stream) {
   if (workspace == nullptr && rows > 0) return SQ_ERR_NULL;
   if (workspace_bytes < sq_workspace_bytes(rows, K)) return SQ_ERR_WORKSPACE;
   const float* act_scale = nullptr;
@@ -228,13 +247,20 @@ int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, in
   // validate the GEMM half before launching anything, so a rejected call leaves no work on the stream
   sq::GemmArgs a = make_args(codes, SQ_CODES_EVEN_ODD, w_packed, w_scales, wscale_mode, row_scales, bias, out, x_dtype,
                              rows, N, K, nullptr);
+  a.activation = activation;
+  a.gate = gate; a.gate_span = gate_span; a.gate_row_stride = gate_row_stride; a.residual = residual;
+  sq::PrepassFusion fusion;
+  fusion.input_activation = input_activation;
+  fusion.norm_kind = norm_kind; fusion.norm_eps = norm_eps; fusion.norm_weight = norm_weight;
+  fusion.mod_scale = mod_scale; fusion.mod_shift = mod_shift; fusion.mod_span = mod_span;
+  fusion.mod_row_stride = mod_row_stride; fusion.round_after = round_after_norm;
   if (rows > 0) {
     int v = sq::validate_gemm(a);
     if (v != SQ_OK) return v;
   }
   int status = sq::launch_prepass(x, x_dtype, rows, K, abits, mode, inv_d, signs, rht_block, act_scale, gain_row, span,
                                   streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
-                                  static_cast<cudaStream_t>(stream));
+                                  static_cast<cudaStream_t>(stream), &fusion);
   if (status != SQ_OK) return status;
   return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
 }

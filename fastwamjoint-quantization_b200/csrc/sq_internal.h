@@ -10,10 +10,23 @@
 
 namespace sq {
 
+// Optional work fused in front of the quantizer: normalisation over the row, AdaLN modulation, rounding.
+struct PrepassFusion {
+  int input_activation = SQ_ACT_FN_NONE;  // applied to x first, result rounded to x's dtype (a module boundary)
+  int norm_kind = SQ_NORM_NONE;      // SQ_NORM_NONE / SQ_NORM_LAYER (no affine) / SQ_NORM_RMS
+  float norm_eps = 0.0f;
+  const void* norm_weight = nullptr; // [K] in x's dtype, or null (RMS only)
+  const void* mod_scale = nullptr;   // AdaLN: y = (1 + scale) * y + shift; rows of K in x's dtype
+  const void* mod_shift = nullptr;
+  int64_t mod_span = 1;              // input rows per modulation row
+  int64_t mod_row_stride = 0;        // elements between modulation rows
+  int round_after = 0;               // round the result to x's dtype before rotation / quantization
+};
+
 int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
                    const float* signs, int rht_block, const float* act_scale, const float* gains, int64_t span,
                    int64_t streams, int64_t seq_tokens, int codes_layout, int pack_int4, void* codes,
-                   float* row_scales, cudaStream_t stream);
+                   float* row_scales, cudaStream_t stream, const PrepassFusion* fusion = nullptr);
 
 struct GemmArgs {
   const int8_t* codes;
@@ -27,6 +40,12 @@ struct GemmArgs {
   int out_dtype;
   int64_t M, N, K;
   int32_t* acc_dump;
+  // fused epilogue: out = residual + gate * act(acc * scales + bias)
+  int activation = SQ_ACT_FN_NONE;
+  const void* gate = nullptr;      // rows of N in out's dtype, one per gate_span output rows
+  int64_t gate_span = 1;
+  int64_t gate_row_stride = 0;     // elements between gate rows
+  const void* residual = nullptr;  // [M, N] in out's dtype
 };
 
 int validate_gemm(const GemmArgs& a);

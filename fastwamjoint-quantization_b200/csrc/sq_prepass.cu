@@ -85,6 +85,15 @@ struct PrepassParams {
   float rht_norm;      // float(1 / sqrt(block))
   int qmax;            // 127 or 7
   int mode, codes_layout, pack_int4;
+  // fused front end
+  int input_activation;
+  int norm_kind;
+  float norm_eps;
+  const void* norm_weight;
+  const void* mod_scale;
+  const void* mod_shift;
+  int64_t mod_span, mod_row_stride;
+  int round_after;
 };
 
 constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23
@@ -94,7 +103,8 @@ __device__ __forceinline__ uint32_t round_code(float q, float qmax) {
   return __float_as_uint(__fadd_rn(fminf(fmaxf(q, -qmax), qmax), kRoundMagic));
 }
 
-template <typename T, int VPT>
+// kFused compiles the normalisation / modulation front end in; the plain pre-pass keeps its register count.
+template <typename T, int VPT, bool kFused>
 __global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) {
   const int tpr = 1 << p.tpr_log2;
   const int t = threadIdx.x & (tpr - 1);
@@ -110,6 +120,88 @@ __global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) 
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (row_ok && vec < vectors) raw = __ldg(xrow + vec);
     Vec8<T>::unpack(raw, v[j]);
+  }
+
+  // sum over the threads of one row (warp shuffle, then one shared-memory hop when a row spans warps)
+  __shared__ float row_partial[32];
+  auto row_sum = [&](float value) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_xor_sync(0xffffffffu, value, offset);
+    if (tpr > 32) {
+      const int warp = threadIdx.x >> 5;
+      __syncthreads();  // the previous use of row_partial is over
+      if ((threadIdx.x & 31) == 0) row_partial[warp] = value;
+      __syncthreads();
+      const int warps_per_row = tpr >> 5;
+      const int first = (warp / warps_per_row) * warps_per_row;
+      value = 0.0f;
+      for (int w = 0; w < warps_per_row; ++w) value += row_partial[first + w];
+    }
+    return value;
+  };
+
+  if (kFused && p.input_activation == SQ_ACT_FN_GELU) {
+    // exact (erf) GELU of the input, rounded to the input type as the output of a separate module would be
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        v[j][i] = 0.5f * v[j][i] * (1.0f + erff(v[j][i] * 0.70710678118654752440f));
+        v[j][i + 1] = 0.5f * v[j][i + 1] * (1.0f + erff(v[j][i + 1] * 0.70710678118654752440f));
+        Vec8<T>::round_trip2(v[j][i], v[j][i + 1]);
+      }
+    }
+  }
+
+  if (kFused && p.norm_kind != SQ_NORM_NONE) {
+    const float inv_k = 1.0f / static_cast<float>(p.K);
+    float mean = 0.0f;
+    if (p.norm_kind == SQ_NORM_LAYER) {
+      float total = 0.0f;
+#pragma unroll
+      for (int j = 0; j < VPT; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) total += v[j][i];  // masked vectors hold zeros
+      mean = row_sum(total) * inv_k;
+    }
+    float squares = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      if (j * tpr + t < vectors) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = v[j][i] - mean;
+          squares = fmaf(d, d, squares);
+        }
+      }
+    }
+    const float rstd = rsqrtf(row_sum(squares) * inv_k + p.norm_eps);
+    const int64_t mod_row = (row_ok ? row : 0) / p.mod_span;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int vec = j * tpr + t;
+      if (vec < vectors) {
+        float w[8], sc[8], sh[8];
+        if (p.norm_weight != nullptr) Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(p.norm_weight) + vec), w);
+        if (p.mod_scale != nullptr) {
+          const T* srow = static_cast<const T*>(p.mod_scale) + mod_row * p.mod_row_stride;
+          const T* hrow = static_cast<const T*>(p.mod_shift) + mod_row * p.mod_row_stride;
+          Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(srow) + vec), sc);
+          Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(hrow) + vec), sh);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float y = (v[j][i] - mean) * rstd;
+          if (p.norm_weight != nullptr) y *= w[i];
+          if (p.mod_scale != nullptr) y = fmaf(y, 1.0f + sc[i], sh[i]);
+          v[j][i] = y;
+        }
+        if (p.round_after) {
+#pragma unroll
+          for (int i = 0; i < 8; i += 2) Vec8<T>::round_trip2(v[j][i], v[j][i + 1]);
+        }
+      }
+    }
   }
 
   if (p.signs != nullptr) {
@@ -244,17 +336,17 @@ __global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) 
   }
 }
 
-template <typename T>
+template <typename T, bool kFused>
 static cudaError_t launch_for_type(const PrepassParams& p, int vpt, dim3 grid, dim3 block, cudaStream_t stream) {
   switch (vpt) {
-    case 1: sq_prepass_kernel<T, 1><<<grid, block, 0, stream>>>(p); break;
-    case 2: sq_prepass_kernel<T, 2><<<grid, block, 0, stream>>>(p); break;
-    case 3: sq_prepass_kernel<T, 3><<<grid, block, 0, stream>>>(p); break;
-    case 4: sq_prepass_kernel<T, 4><<<grid, block, 0, stream>>>(p); break;
-    case 5: sq_prepass_kernel<T, 5><<<grid, block, 0, stream>>>(p); break;
-    case 6: sq_prepass_kernel<T, 6><<<grid, block, 0, stream>>>(p); break;
-    case 7: sq_prepass_kernel<T, 7><<<grid, block, 0, stream>>>(p); break;
-    default: sq_prepass_kernel<T, 8><<<grid, block, 0, stream>>>(p); break;
+    case 1: sq_prepass_kernel<T, 1, kFused><<<grid, block, 0, stream>>>(p); break;
+    case 2: sq_prepass_kernel<T, 2, kFused><<<grid, block, 0, stream>>>(p); break;
+    case 3: sq_prepass_kernel<T, 3, kFused><<<grid, block, 0, stream>>>(p); break;
+    case 4: sq_prepass_kernel<T, 4, kFused><<<grid, block, 0, stream>>>(p); break;
+    case 5: sq_prepass_kernel<T, 5, kFused><<<grid, block, 0, stream>>>(p); break;
+    case 6: sq_prepass_kernel<T, 6, kFused><<<grid, block, 0, stream>>>(p); break;
+    case 7: sq_prepass_kernel<T, 7, kFused><<<grid, block, 0, stream>>>(p); break;
+    default: sq_prepass_kernel<T, 8, kFused><<<grid, block, 0, stream>>>(p); break;
   }
   return cudaGetLastError();
 }
@@ -262,8 +354,15 @@ static cudaError_t launch_for_type(const PrepassParams& p, int vpt, dim3 grid, d
 int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
                    const float* signs, int rht_block, const float* act_scale, const float* gains, int64_t span,
                    int64_t streams, int64_t seq_tokens, int codes_layout, int pack_int4, void* codes,
-                   float* row_scales, cudaStream_t stream) {
+                   float* row_scales, cudaStream_t stream, const PrepassFusion* fusion) {
   if (x == nullptr || codes == nullptr || row_scales == nullptr) return SQ_ERR_NULL;
+  PrepassFusion none;
+  const PrepassFusion& f = fusion != nullptr ? *fusion : none;
+  if (f.norm_kind != SQ_NORM_NONE && f.norm_kind != SQ_NORM_LAYER && f.norm_kind != SQ_NORM_RMS) return SQ_ERR_ENUM;
+  if ((f.mod_scale == nullptr) != (f.mod_shift == nullptr)) return SQ_ERR_NULL;
+  if (f.norm_kind == SQ_NORM_NONE && (f.mod_scale != nullptr || f.norm_weight != nullptr)) return SQ_ERR_ENUM;
+  if (f.input_activation != SQ_ACT_FN_NONE && f.input_activation != SQ_ACT_FN_GELU) return SQ_ERR_ENUM;
+  if (f.mod_scale != nullptr && (f.mod_span <= 0 || f.mod_row_stride < K || (f.mod_row_stride & 7) != 0)) return SQ_ERR_SHAPE;
   if (x_dtype != SQ_BF16 && x_dtype != SQ_FP16) return SQ_ERR_ENUM;
   if (abits != 8 && abits != 4) return SQ_ERR_ENUM;
   if (mode != SQ_ACT_STATIC && mode != SQ_ACT_TOKEN) return SQ_ERR_ENUM;
@@ -300,11 +399,21 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
   p.span = span; p.streams = streams; p.seq_tokens = seq_tokens;
   p.tpr_log2 = tpr_log2; p.rht_lanes_log2 = lanes_log2; p.rht_norm = norm;
   p.qmax = abits == 8 ? 127 : 7; p.mode = mode; p.codes_layout = codes_layout; p.pack_int4 = pack_int4;
+  p.input_activation = f.input_activation;
+  p.norm_kind = f.norm_kind; p.norm_eps = f.norm_eps; p.norm_weight = f.norm_weight;
+  p.mod_scale = f.mod_scale; p.mod_shift = f.mod_shift;
+  p.mod_span = f.mod_span > 0 ? f.mod_span : 1; p.mod_row_stride = f.mod_row_stride; p.round_after = f.round_after;
 
   const dim3 grid(static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta));
   const dim3 block(threads);
-  cudaError_t err = x_dtype == SQ_BF16 ? launch_for_type<__nv_bfloat16>(p, vpt, grid, block, stream)
-                                       : launch_for_type<__half>(p, vpt, grid, block, stream);
+  cudaError_t err;
+  if (f.norm_kind != SQ_NORM_NONE || f.input_activation != SQ_ACT_FN_NONE) {
+    err = x_dtype == SQ_BF16 ? launch_for_type<__nv_bfloat16, true>(p, vpt, grid, block, stream)
+                             : launch_for_type<__half, true>(p, vpt, grid, block, stream);
+  } else {
+    err = x_dtype == SQ_BF16 ? launch_for_type<__nv_bfloat16, false>(p, vpt, grid, block, stream)
+                             : launch_for_type<__half, false>(p, vpt, grid, block, stream);
+  }
   return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
 }
 

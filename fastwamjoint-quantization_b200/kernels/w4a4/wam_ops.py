@@ -7,7 +7,8 @@ from __future__ import annotations
 
 import torch
 
-from .._common import GROUP, check_common, dynamic_linear, scheduled_linear, stream_span
+from .._common import (GROUP, adaln_linear, check_common, dynamic_linear, gate_residual_linear, scheduled_linear,
+                       stream_span)
 from .loader import load_extension  # noqa: F401
 
 
@@ -47,9 +48,13 @@ def symmetric_dynamic_linear(x, packed, scales, bias, inverse, signs=None, *, rh
 
 def symmetric_scheduled_stream_adaln_linear(x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
                                             call, adaln_scale, adaln_shift, epsilon):
-    raise NotImplementedError("The AdaLN block fusion (wam_ops.py:78-96) is not built yet; call the unfused linear.")
+    """Affine-free LayerNorm and the MLP AdaLN moved into the activation producer."""
+    return adaln_linear("W4A4", 256, 4, x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
+                        call, adaln_scale, adaln_shift, epsilon)
 
 
 def symmetric_scheduled_stream_gate_residual_linear(x, packed, scales, bias, inverse, activation_scales, gains,
                                                     token_counts, call, residual, gate):
-    raise NotImplementedError("The gate/residual block fusion (wam_ops.py:99-118) is not built yet; call the unfused linear.")
+    """``x + gate * projection`` moved into the GEMM epilogue."""
+    return gate_residual_linear("W4A4", 256, 4, x, packed, scales, bias, inverse, activation_scales, gains,
+                                token_counts, call, residual, gate)

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from .._common import check_common, dynamic_linear, scheduled_linear, stream_span
+from .._common import adaln_linear, check_common, dynamic_linear, gate_residual_linear, scheduled_linear, stream_span
 from .loader import load_extension  # noqa: F401  (part of the reference's surface)
 
 
@@ -38,9 +38,13 @@ def symmetric_scheduled_stream_linear(x, packed, scales, bias, inverse, activati
 
 def symmetric_scheduled_stream_adaln_linear(x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
                                             call, adaln_scale, adaln_shift, epsilon):
-    raise NotImplementedError("The AdaLN block fusion (ops.py:66-84) is not built yet; call the unfused linear.")
+    """Affine-free LayerNorm and the MLP AdaLN moved into the activation producer."""
+    return adaln_linear("W4A8", 32, 8, x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
+                        call, adaln_scale, adaln_shift, epsilon)
 
 
 def symmetric_scheduled_stream_gate_residual_linear(x, packed, scales, bias, inverse, activation_scales, gains,
                                                     token_counts, call, residual, gate):
-    raise NotImplementedError("The gate/residual block fusion (ops.py:87-105) is not built yet; call the unfused linear.")
+    """``x + gate * projection`` moved into the GEMM epilogue."""
+    return gate_residual_linear("W4A8", 32, 8, x, packed, scales, bias, inverse, activation_scales, gains,
+                                token_counts, call, residual, gate)

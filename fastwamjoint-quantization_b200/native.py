@@ -76,12 +76,31 @@ def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_
     return (out, acc) if want_accumulators else out
 
 
+def _rows_view(t: torch.Tensor, width: int, name: str):
+    """(data pointer, row stride in elements, rows) of a tensor whose last axis is contiguous and whose leading
+    axes collapse to evenly strided rows - e.g. the strided slice ``modulation[:, 0]`` of a [groups, 6, width] tensor."""
+    if t.shape[-1] != width or t.stride(-1) != 1:
+        raise ValueError(f"{name} must have a contiguous last axis of {width} elements.")
+    flat = t.reshape(-1, width) if t.is_contiguous() else t
+    if flat.ndim != 2:
+        raise ValueError(f"{name} must be viewable as evenly strided rows.")
+    return flat.data_ptr(), (flat.stride(0) if flat.shape[0] > 1 else width), flat.shape[0]
+
+
 def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, *, abits: int, mode: str,
            inverse=None, signs=None, rht_block: int = 128, act_scales=None, gains=None, call: int = 0,
            span: int = 1, streams: int = 1, out: torch.Tensor | None = None,
-           workspace: torch.Tensor | None = None) -> torch.Tensor:
-    """One whole quantized linear (pre-pass + GEMM) through ``sq_linear``.  ``out`` and ``workspace``
-    (uint8, at least ``sq_workspace_bytes(rows, K)``) may be passed to reuse buffers across calls."""
+           workspace: torch.Tensor | None = None, norm: str | None = None, norm_eps: float = 1e-6, norm_weight=None,
+           mod_scale=None, mod_shift=None, round_after_norm: bool = False, activation: str | None = None,
+           gate=None, residual=None, input_activation: str | None = None) -> torch.Tensor:
+    """One whole quantized linear (pre-pass + GEMM) through ``sq_linear_fused``.  ``out`` and ``workspace``
+    (uint8, at least ``sq_workspace_bytes(rows, K)``) may be passed to reuse buffers across calls.
+
+    Optional fused work: ``input_activation="gelu"`` applied to x first (rounded to x's dtype); ``norm`` ("layer" without affine, or "rms" with optional ``norm_weight``) and AdaLN
+    modulation ``(1 + mod_scale) * y + mod_shift`` in front of the quantizer (one modulation row per equal
+    share of the input rows), optionally rounded to x's dtype (``round_after_norm``); ``activation="gelu"``,
+    ``gate`` (one row per equal share of the output rows) and ``residual`` behind the GEMM:
+    ``out = residual + gate * act(linear(x))``."""
     _require_cuda(x, "x")
     x = x.contiguous()
     k = x.shape[-1]
@@ -99,15 +118,39 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
         raise RuntimeError("out must be a contiguous tensor of shape x.shape[:-1] + (N,) in x's dtype.")
     group = w_scales.dtype == torch.float16
     calls = 0 if act_scales is None else act_scales.numel()
+    norm_kind = {None: _lib.NORM_NONE, "layer": _lib.NORM_LAYER, "rms": _lib.NORM_RMS}[norm]
+    mod_ptr = shift_ptr = gate_ptr = None
+    mod_span = gate_span = 1
+    mod_stride = gate_stride = 0
+    if mod_scale is not None:
+        mod_ptr, mod_stride, mod_rows = _rows_view(mod_scale, k, "mod_scale")
+        shift_ptr, shift_stride, shift_rows = _rows_view(mod_shift, k, "mod_shift")
+        if shift_stride != mod_stride or shift_rows != mod_rows or rows % mod_rows:
+            raise ValueError("AdaLN scale and shift must share a layout and cover complete input rows.")
+        mod_span = rows // mod_rows
+    if gate is not None:
+        gate_ptr, gate_stride, gate_rows = _rows_view(gate, n, "gate")
+        if rows % gate_rows:
+            raise ValueError("Gate groups must cover complete output rows.")
+        gate_span = rows // gate_rows
+    if residual is not None:
+        residual = residual.contiguous()
     with torch.cuda.device(x.device):
-        status = lib.sq_linear(
+        status = lib.sq_linear_fused(
             x.data_ptr(), _DTYPES[x.dtype], rows, k, n, int(abits),
             _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
             _ptr(inverse), _ptr(signs), int(rht_block), _ptr(act_scales), _ptr(gains), int(calls), int(call),
             int(span), int(streams), int(x.shape[-2]),
             packed.data_ptr(), w_scales.data_ptr(), _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32,
-            _ptr(bias), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
-    _lib.check(status, "sq_linear")
+            _ptr(bias), _lib.ACT_FN_GELU if input_activation == "gelu" else _lib.ACT_FN_NONE, norm_kind, float(norm_eps), _ptr(norm_weight), mod_ptr, shift_ptr, int(mod_span),
+            int(mod_stride), int(bool(round_after_norm)),
+            _lib.ACT_FN_NONE, gate_ptr, int(gate_span), int(gate_stride),
+            _ptr(residual), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
+    _lib.check(status, "sq_linear_fused")
+    if activation == "gelu":  # an output activation is not fused into the GEMM (it measured slower there)
+        if gate is not None or residual is not None:
+            raise ValueError("an output activation cannot be combined with a fused gate or residual.")
+        out = torch.nn.functional.gelu(out)
     return out
 
 

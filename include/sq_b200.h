@@ -45,6 +45,15 @@ extern "C" {
 #define SQ_CODES_NATURAL 0 /* k, k+1, ..., k+7                                                     */
 #define SQ_CODES_EVEN_ODD 1 /* k, k+2, k+4, k+6, k+1, k+3, k+5, k+7 (what sq_gemm unpacks fastest) */
 
+/* normalisation fused in front of the quantizer (sq_linear_fused) */
+#define SQ_NORM_NONE 0
+#define SQ_NORM_LAYER 1 /* (x - mean) * rsqrt(var + eps), no affine (the reference's fused AdaLN producer) */
+#define SQ_NORM_RMS 2   /* x * rsqrt(mean(x^2) + eps) [* weight] */
+
+/* activation fused in front of the quantizer or behind the GEMM (sq_linear_fused) */
+#define SQ_ACT_FN_NONE 0
+#define SQ_ACT_FN_GELU 1 /* exact (erf) GELU */
+
 /* weight-scale forms */
 #define SQ_WSCALE_CHANNEL_F32 0 /* float  [N]          (reference: checkpoint.py:49-50, runtime.py:89) */
 #define SQ_WSCALE_GROUP_F16 1   /* __half [N, K / 128] (group-128 scheme of the benchmark)             */
@@ -128,6 +137,30 @@ int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, in
               int64_t span, int64_t streams, int64_t seq_tokens,
               const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
               void* out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* sq_linear with work of the surrounding block folded into its two kernels.
+ * Pre-pass side, replaces quantize_static_adaln_stream_kernel / quantize_dynamic_adaln_per_token_kernel
+ * (w4a8.cu:519-691) and their int4 forms (w4a4.cu:963-1049, 1126-1211): optionally an activation of the input
+ * (input_activation, SQ_ACT_FN_*, result rounded to x's dtype), then a normalisation of each row
+ * (norm_kind, norm_eps, optional norm_weight [K] for RMS), then y = (1 + mod_scale) * y + mod_shift with one
+ * modulation row per mod_span input rows (rows mod_row_stride elements apart; both null for none), optionally
+ * rounded to x's dtype (round_after_norm, what an unfused module boundary would do), then the pre-pass proper.
+ * GEMM side, replaces GatedResidualEpilogueGemm (w4a8.cu:383-479): out = residual + gate * linear, with gate rows
+ * of N (one per gate_span output rows, gate_row_stride elements apart, null for none) and residual [rows, N]
+ * (null for none), all in fp32 before the single rounding to out's dtype.  `activation` must be
+ * SQ_ACT_FN_NONE: an activation is fused on the input side of the linear that consumes it (input_activation),
+ * where it costs nothing; in the GEMM epilogue it measured slower than a separate kernel. */
+int sq_linear_fused(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+                    const float* inv_d, const float* signs, int rht_block,
+                    const float* act_scales, const float* gains, int64_t calls, int64_t call,
+                    int64_t span, int64_t streams, int64_t seq_tokens,
+                    const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
+                    int input_activation, int norm_kind, float norm_eps, const void* norm_weight,
+                    const void* mod_scale, const void* mod_shift, int64_t mod_span, int64_t mod_row_stride,
+                    int round_after_norm,
+                    int activation, const void* gate, int64_t gate_span, int64_t gate_row_stride,
+                    const void* residual,
+                    void* out, void* workspace, size_t workspace_bytes, void* stream);
 
 /* sq_linear for callers that cannot allocate device memory.  It has no counterpart in the reference, whose
  * operators always allocate their scratch per call (torch::empty, w4a8.cu:1358-1360).

@@ -243,3 +243,105 @@ def test_small_dit_stack_native_vs_reference_and_graph(m, abits, rotate):
         graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(captured, native_out)
+
+
+def _w4a4_inputs(dtype, rows, k, n):
+    """Inputs of the reference's W4A4 tests (tests/test_wam_w4a4.py:17-29), generated on the CPU."""
+    gen = torch.Generator().manual_seed(rows + k + n)
+    x = (torch.randn(1, rows, k, generator=gen) * 0.5).to(dtype)
+    qw = torch.randint(-7, 8, (n, k), generator=gen, dtype=torch.int8)
+    ws = torch.full((n,), 1 / 512)
+    inverse = torch.pow(2.0, torch.randint(-1, 2, (k,), generator=gen).float())
+    bias = (torch.randn(n, generator=gen) * 0.01).to(dtype)
+    counts = (16, 16) if rows == 32 else (98, 98, 98)
+    gains = torch.ones(10, len(counts))
+    gains[9] = torch.tensor([2.0, 0.5, 1.0][: len(counts)])
+    scales = torch.linspace(0.125, 0.25, 10)
+    return x, qw, ws, bias, inverse, scales, gains, counts, gen
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,k,n", [(32, 1024, 4096), (294, 3072, 14336)])
+def test_adaln_fusion(m, oracle, dtype, rows, k, n):
+    """tests/test_wam_w4a4.py:61-86: LayerNorm without affine and AdaLN folded into the pre-pass, modulation given
+    as strided views; relative RMS < 0.003 against the unfused kernel-order oracle; graph replay bit-equal."""
+    ops = m["ops4"]
+    x, qw, ws, bias, inv, scales, gains, counts, gen = _w4a4_inputs(dtype, rows, k, n)
+    modulation = (torch.randn(len(counts), 6, k, generator=gen) * 0.1).to(dtype)
+    cuda = lambda t: t.cuda()
+    mod = cuda(modulation)
+    scale, shift = mod[:, 0], mod[:, 1]
+    assert not scale.is_contiguous()
+    packed = m["ops8"].pack_signed_int4(qw).cuda()
+    args = (cuda(x), packed, cuda(ws), cuda(bias), cuda(inv), cuda(scales), cuda(gains), counts, 9)
+    actual = ops.symmetric_scheduled_stream_adaln_linear(*args, scale, shift, 1e-6)
+    xf = x.float()
+    normalized = (xf - xf.mean(-1, keepdim=True)) * torch.rsqrt(xf.var(-1, unbiased=False, keepdim=True) + 1e-6)
+    transformed = (normalized * (1 + modulation[:, 0].float().repeat_interleave(counts[0], 0))
+                   + modulation[:, 1].float().repeat_interleave(counts[0], 0))
+    # the oracle quantizes x.float(); feed it the transformed row in fp32 (no rounding, as the fused kernel)
+    want = oracle.static_codes(transformed, bits=4, inverse=inv, activation_scales=scales, gains=gains,
+                               token_counts=counts, call=9)
+    acc = oracle.group_accumulators(want[0].reshape(-1, k), qw, None)[..., 0]
+    expected = oracle.epilogue_channel(acc, ws, want[1], bias, dtype).reshape(1, rows, n)
+    rel = (actual.cpu().float() - expected.float()).square().mean().sqrt() / expected.float().square().mean().sqrt()
+    assert rel < 0.003, float(rel)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = ops.symmetric_scheduled_stream_adaln_linear(*args, scale, shift, 1e-6)
+    graph.replay()
+    torch.testing.assert_close(captured, actual, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,k,n", [(32, 4096, 1024), (294, 14336, 3072)])
+@pytest.mark.parametrize("abits", [4, 8])
+def test_gate_residual_fusion(m, oracle, dtype, rows, k, n, abits):
+    """tests/test_wam_w4a4.py:89-103: residual + gate * projection in the GEMM epilogue, strided gate view;
+    rtol 0.008, atol 0.001 against the kernel-order oracle."""
+    ops = m["ops4"] if abits == 4 else m["ops8"]
+    x, qw, ws, bias, inv, scales, gains, counts, gen = _w4a4_inputs(dtype, rows, k, n)
+    if abits == 8:
+        scales = scales / 16
+    residual = torch.randn(1, rows, n, generator=gen).to(dtype)
+    gate_full = (torch.randn(len(counts), 6, n, generator=gen) * 0.1).to(dtype)
+    gate = gate_full.cuda()[:, 0]
+    assert not gate.is_contiguous()
+    cuda = lambda t: t.cuda()
+    packed = m["ops8"].pack_signed_int4(qw).cuda()
+    args = (cuda(x), packed, cuda(ws), cuda(bias), cuda(inv), cuda(scales), cuda(gains), counts, 9)
+    residual_cuda = cuda(residual)
+    actual = ops.symmetric_scheduled_stream_gate_residual_linear(*args, residual_cuda, gate)
+    codes, row_scales = oracle.static_codes(x, bits=abits, inverse=inv, activation_scales=scales, gains=gains,
+                                            token_counts=counts, call=9)
+    acc = oracle.group_accumulators(codes.reshape(-1, k), qw, None)[..., 0]
+    plain = acc.float() * row_scales.float().reshape(-1, 1) * ws.float() + bias.float()
+    expected = (plain * gate_full[:, 0].float().repeat_interleave(counts[0], 0) + residual.float()[0]).to(dtype)
+    torch.testing.assert_close(actual.cpu()[0], expected, rtol=0.008, atol=0.001)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = ops.symmetric_scheduled_stream_gate_residual_linear(*args, residual_cuda, gate)
+    graph.replay()
+    torch.testing.assert_close(captured, actual, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("abits,rotate", [(8, False), (4, True)])
+def test_fused_rmsnorm_gelu_residual_match_the_unfused_composition(m, abits, rotate):
+    """RMSNorm in the pre-pass, GELU and residual in the epilogue against the same layer fed by torch ops:
+    the pre-pass rounds the normalised row to bf16 like a separate module, so codes agree except where the two
+    reductions of the mean differ in the last bit; outputs within 1e-2 relative Frobenius error."""
+    D = m["dit"]
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    w = (torch.randn(768, 512, generator=gen, device="cuda") * 0.02).bfloat16()
+    layer = D.TokenQuantLinear(w, activation_bits=abits, rotate=rotate, module_name="fused", backend="native")
+    x = torch.randn(1, 200, 512, generator=gen, device="cuda").bfloat16() * 3
+    res = torch.randn(1, 200, 768, generator=gen, device="cuda").bfloat16()
+    with torch.no_grad():
+        fused = layer(x, rms_eps=1e-6, activation="gelu", residual=res)
+        unfused = res + F.gelu(layer(D.rms_norm(x, 1e-6)))
+        pre = layer(x, input_activation="gelu")
+        assert torch.equal(pre, layer(F.gelu(x)))  # GELU in the pre-pass: same codes, same output
+        layer.backend = "reference"
+        reference = layer(x, rms_eps=1e-6, activation="gelu", residual=res)
+    assert ((fused.float() - unfused.float()).norm() / unfused.float().norm()).item() < 1e-2
+    assert ((fused.float() - reference.float()).norm() / reference.float().norm()).item() < 1e-2

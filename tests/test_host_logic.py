@@ -132,8 +132,9 @@ def test_operator_argument_checks_raise_value_errors(pkg, oracle):
     with pytest.raises(ValueError, match="CUDA"):
         wam.symmetric_scheduled_stream_linear(x, packed, torch.ones(8), None, torch.ones(256), torch.ones(2),
                                               torch.ones(2, 2), (2, 2), 0)
-    with pytest.raises(NotImplementedError):
-        ops.symmetric_scheduled_stream_adaln_linear(x, packed, None, None, None, None, None, (2, 2), 0, None, None, 1e-6)
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.symmetric_scheduled_stream_adaln_linear(x, packed, torch.ones(8), None, torch.ones(256), torch.ones(2),
+                                                    torch.ones(2, 2), (2, 2), 0, x[0, :2], x[0, :2], 1e-6)
     assert ops.load_extension.cache_info().currsize == 0  # never loaded on a box without CUDA
 
 
