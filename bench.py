@@ -482,7 +482,8 @@ def main():
 
     def gemm_only(i):
         j = i % nsets
-        native.gemm(pre[j][0], packs[j], wss[j], pre[j][1], bias, out_dtype=torch.bfloat16, out=outs[j])
+        native.gemm(pre[j][0], packs[j], wss[j], pre[j][1], bias, out_dtype=torch.bfloat16, out=outs[j],
+                    int4_range=abits == 4)  # what sq_linear passes for the codes of a 4-bit pre-pass
 
     def prepass_only(i):
         j = i % nsets

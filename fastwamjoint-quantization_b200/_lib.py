@@ -19,6 +19,7 @@ NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024 + 65536
 BF16, FP16 = 0, 1
 ACT_STATIC, ACT_TOKEN = 0, 1
 CODES_NATURAL, CODES_EVEN_ODD = 0, 1
+CODES_INT4_RANGE = 2  # OR-ed onto the layout for sq_gemm: every code lies in [-8, 7]
 WSCALE_CHANNEL_F32, WSCALE_GROUP_F16 = 0, 1
 NORM_NONE, NORM_LAYER, NORM_RMS = 0, 1, 2
 ACT_FN_NONE, ACT_FN_GELU = 0, 1

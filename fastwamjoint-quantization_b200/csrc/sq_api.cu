@@ -167,7 +167,8 @@ static sq::GemmArgs make_args(const void* codes, int codes_layout, const void* w
                               int64_t M, int64_t N, int64_t K, int32_t* acc_dump) {
   sq::GemmArgs a;
   a.codes = static_cast<const int8_t*>(codes);
-  a.codes_layout = codes_layout;
+  a.codes_layout = codes_layout & ~SQ_CODES_INT4_RANGE;
+  a.codes_int4_range = (codes_layout & SQ_CODES_INT4_RANGE) != 0;
   a.w_packed = static_cast<const uint8_t*>(w_packed);
   a.w_scales = w_scales;
   a.wscale_mode = wscale_mode;
@@ -245,7 +246,8 @@ int sq_linear_fused(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t
   float* row_scales = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
                                                sq::round256(static_cast<size_t>(rows) * static_cast<size_t>(K)));
   // validate the GEMM half before launching anything, so a rejected call leaves no work on the stream
-  sq::GemmArgs a = make_args(codes, SQ_CODES_EVEN_ODD, w_packed, w_scales, wscale_mode, row_scales, bias, out, x_dtype,
+  // the pre-pass clamps 4-bit codes to +-7, so the GEMM may use its small accumulator offset
+  sq::GemmArgs a = make_args(codes, SQ_CODES_EVEN_ODD | (abits == 4 ? SQ_CODES_INT4_RANGE : 0), w_packed, w_scales, wscale_mode, row_scales, bias, out, x_dtype,
                              rows, N, K, nullptr);
   a.activation = activation;
   a.gate = gate; a.gate_span = gate_span; a.gate_row_stride = gate_row_stride; a.residual = residual;

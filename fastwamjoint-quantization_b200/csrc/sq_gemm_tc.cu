@@ -5,18 +5,22 @@
 // output channel, so the per-group weight scale is a per-thread scalar when the accumulator is
 // drained, and small token counts map to a small UMMA N instead of a wasted 128-row tile.
 //
-// Per CTA (persistent over tiles, 512 threads = 4 warpgroups):
+// Per CTA (persistent over tiles, 768 threads):
 //   warp 0        TMA producer: per 128-K block one box of packed int4 weights [128 ch x 64 B] and one
-//                 box of int8 activation codes [TOK x 128 B, 128-byte swizzle]
-//   warp 1        allocates TMEM, issues tcgen05.mma.kind::i8 (4 x K=32 per block), commits to mbarriers
+//                 box of int8 activation codes [tokens x 128 B, 128-byte swizzle]
+//   warps 1-3     issue tcgen05.mma.kind::i8 (4 x K=32 per block) and commit to mbarriers; in the group form
+//                 they take the groups round-robin, in the channel form warp 1 works alone.  Warp 1 owns TMEM.
 //   warps 4-7     unpack int4 -> int8 from the packed stage into the canonical K-major 128B-swizzled
 //                 operand tile (nibble v becomes the int8 value 16 v; the factor 1/16 is exact and is
 //                 folded into the scale)
-//   warps 8-15    drain: tcgen05.ld the int32 accumulator of one weight group, convert, multiply by
-//                 the group scale, add into fp32 sums in registers; after the last group apply the row
-//                 scale and bias and store bf16/fp16
-// TMEM holds a ring of 3 or 4 accumulators, so the MMA warp runs ahead of the drain; the drain in turn
-// issues the TMEM loads of group g+1 while it does the arithmetic of group g.
+//   warps 8-23    drain, four warps per TMEM lane quarter, each owning a slice of the token columns:
+//                 tcgen05.ld the int32 accumulator of one weight group, hand the accumulator back, fold it
+//                 into fp32 sums in registers with the group scale; after the last group apply the row
+//                 scale, bias, gate and residual and store bf16/fp16
+// TMEM holds a ring of four accumulators, so the MMA warps run ahead of the drain.
+//
+// The group form is bound by the instructions the drain issues per accumulator element, so the integer to float
+// conversion is done by the tensor core itself: see the note at kConstTileBytes.
 //
 // Every mbarrier wait is time-bounded (see sq_ptx.cuh); a wait that gives up sets the CTA's abort
 // flag and the device status word, all roles leave their loops, TMEM is released, the kernel returns.
@@ -48,19 +52,28 @@ constexpr int kTraceSlots = 512;
 enum TraceRole { kTrTmaIssue = 0, kTrConvStart, kTrConvDone, kTrMmaAccFree, kTrMmaIssue, kTrDrainStart,
                  kTrDrainRelease, kTrDrainDone, kTrMmaCommitted, kTraceRoles };
 
-constexpr uint32_t kMagicBits = 0x4B400000u;  // bit pattern of the float 12582912 = 1.5 * 2^23
-constexpr float kMagicFloat = 12582912.0f;
+// Group mode keeps every accumulator positive: before the real MMAs of a group, MMAs of a constant tile (both
+// operands the same bytes c) put 32 c^2 per MMA into each element.  A positive int32 below 2^23 read as a float
+// is the denormal acc * 2^-149, so the conversion to float costs no instruction at all: the drain is one packed
+// FFMA per two elements with the scale pre-multiplied by 2^96.
+//   any int8 codes:      16 |sum w a| over one 128-K group is at most 16 * 8 * 128 * 128 = 2^21, reached only by
+//                        w = a = minimum, which is positive; c = -128, four MMAs: offset 2^21, sums below 2^22 + 1
+//   codes within [-8, 7]: 16 |sum w a| <= 16 * 8 * 8 * 128 = 2^17, the negative side stays above -2^17;
+//                        c = 64, one MMA: offset 2^17 (a smaller offset also costs less fp32 precision)
+constexpr uint32_t kConstTileBytes = kBlockCh * kBlockK;  // 16 KiB
+constexpr float kScaleUp = 7.922816251426434e28f;    // 2^96: keeps acc * 2^-149 * scale a normal float
+constexpr float kScaleDown = 562949953421312.0f;     // 2^49 = 2^149 / 2^96 / 16 (the unpacked weights are 16 w)
 
 constexpr int kNumConverterWarps = 4;
 constexpr int kNumDrainWarps = 16;  // four per TMEM lane quarter, each owns a slice of the token columns
 
 __host__ __device__ constexpr int stages_for(int tok) {
   // shared memory per stage: unpacked weights + codes + packed weights
-  return tok == 128 ? 5 : tok == 64 ? 7 : 8;
+  return tok == 128 ? 5 : tok == 64 ? 6 : 7;
 }
 __host__ __device__ constexpr uint32_t stage_bytes(int tok) { return kWBytes + tok * kBlockK + kPackedBytes; }
 __host__ __device__ constexpr uint32_t smem_bytes_for(int tok) {
-  return stages_for(tok) * stage_bytes(tok) + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  return stages_for(tok) * stage_bytes(tok) + kConstTileBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
 }
 
 struct TcParams {
@@ -75,6 +88,9 @@ struct TcParams {
   int ch_tiles, tok_tiles, k_blocks;
   int tok_tile;   // tokens per tile at run time: a multiple of 16, <= TOK
   int slice_cols;  // token columns per drain warp: drain warp j of a lane quarter owns [j, j + 1) * slice_cols
+  int offset_steps;     // group mode: constant-tile MMAs in front of every group (1 or 4)
+  uint32_t offset_word;  // four copies of the constant tile's byte
+  uint32_t offset_bits;  // what those MMAs add to every accumulator element
   int out_dtype;
   // fused epilogue: out = residual + gate * act(linear)
   int activation;
@@ -100,6 +116,20 @@ template <int kRegs>
 __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs)); }
 template <int kRegs>
 __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs)); }
+
+// (c0, c1) += (a0, a1) * s as one packed single-precision FMA; a0 / a1 are raw bit patterns
+__device__ __forceinline__ void ffma2(float& c0, float& c1, uint32_t a0, uint32_t a1, float s) {
+  asm("{\n\t"
+      ".reg .b64 a, b, c;\n\t"
+      "mov.b64 a, {%2, %3};\n\t"
+      "mov.b64 b, {%4, %4};\n\t"
+      "mov.b64 c, {%0, %1};\n\t"
+      "fma.rn.f32x2 c, a, b, c;\n\t"
+      "mov.b64 {%0, %1}, c;\n\t"
+      "}\n"
+      : "+f"(c0), "+f"(c1)
+      : "r"(a0), "r"(a1), "f"(s));
+}
 
 __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code) {
   *abort_flag = 1;
@@ -134,7 +164,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   const uint32_t w_ring = smem_base;                  // S x 16 KiB, unpacked weights (UMMA A)
   const uint32_t x_ring = w_ring + S * kWBytes;       // S x TOK*128, codes (UMMA B)
   const uint32_t p_ring = x_ring + S * kXBytes;       // S x 8 KiB, packed weights
-  const uint32_t bars = p_ring + S * kPackedBytes;    // mbarriers, 8 B each
+  const uint32_t c_tile = p_ring + S * kPackedBytes;  // 16 KiB of 0x80: both operands of the offset MMAs
+  const uint32_t bars = c_tile + kConstTileBytes;     // mbarriers, 8 B each
   const uint32_t bar_full = bars;                     // [S] TMA landed (tx bytes)
   const uint32_t bar_wfull = bars + 8 * S;            // [S] converters wrote W[s]
   const uint32_t bar_empty = bars + 16 * S;           // [S] MMAs reading stage s retired
@@ -167,6 +198,11 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
+  }
+  if (kGroup) {
+    uint32_t* c_words = reinterpret_cast<uint32_t*>(smem_gen + (c_tile - smem_base));
+    for (uint32_t i = threadIdx.x; i < kConstTileBytes / 4; i += kThreads) c_words[i] = p.offset_word;
+    fence_proxy_async_smem();  // the tensor core reads this tile through the async proxy
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -240,6 +276,15 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           }
           if (warp == 1 && lane == 0) stamp(kTrMmaAccFree, git);
           const uint32_t tmem_d = tmem_base + buf * kBufStride;
+          if (kGroup) {
+            // the offset MMAs need no operand from the pipeline: they start the accumulator at a positive value
+            tc_fence_after_sync();
+            if (elect_one()) {
+              const uint64_t desc_c = umma_desc_k128(c_tile);
+              for (int b = 0; b < p.offset_steps; ++b) umma_i8(tmem_d, desc_c, desc_c, idesc, b > 0 ? 1u : 0u);
+            }
+            __syncwarp();
+          }
           for (int kb = 0; kb < blocks_per_group; ++kb, ++it) {
             const uint32_t s = it % S, phase = (it / S) & 1u;
             if (!mbar_wait_bounded(bar_wfull + 8 * s, phase, abort_flag, kWaitLimitNs)) {
@@ -254,7 +299,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
 #pragma unroll
               for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                const uint32_t accumulate = (kGroup || kb > 0 || k > 0) ? 1u : 0u;
                 // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in the (address >> 4) field
                 umma_i8(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
               }
@@ -341,6 +386,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);
     }
     const __half* scale_row = static_cast<const __half*>(p.w_scales);
+    const uint32_t offset_bits = kGroup ? p.offset_bits : 0u;
+    const float offset_float = __uint_as_float(offset_bits);
 
     uint32_t git = 0;
     bool ok = true;
@@ -356,6 +403,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       float sums[kCols];
 #pragma unroll
       for (int i = 0; i < kCols; ++i) sums[i] = 0.0f;
+      float offset_sum = 0.0f;  // what the constant offsets added to every sum of this channel
 
       // group scales are fetched two groups ahead as raw fp16 bits and converted when used, so the
       // global-load latency never sits in front of a drain
@@ -369,7 +417,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const uint32_t buf = git % kAccBufs, aphase = (git / kAccBufs) & 1u;
         float scale = 0.0625f;  // the unpacked weights are 16 x the int4 value
         if (kGroup) {
-          scale = __half2float(__ushort_as_half(raw0)) * 0.0625f;
+          scale = __half2float(__ushort_as_half(raw0)) * kScaleUp;
+          offset_sum = fmaf(offset_float, scale, offset_sum);
           raw0 = raw1;
           if (g + 2 < groups && n_ok)
             raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + g + 2);
@@ -394,20 +443,23 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
         if (my_cols > 0) {
 #pragma unroll
-          for (int i = 0; i < kCols; ++i) {
-            // group mode: |16 acc| < 2^22 inside one 128-K group, so adding the bit pattern of 1.5 * 2^23
-            // gives the float 12582912 + 16 acc exactly: int -> float is an integer add and a float
-            // subtract (full rate) instead of a conversion instruction (a sixteenth of the rate)
-            const float value = kGroup ? __fadd_rn(__uint_as_float(r[i] + kMagicBits), -kMagicFloat)
-                                       : static_cast<float>(static_cast<int32_t>(r[i]));
-            sums[i] = fmaf(value, scale, sums[i]);
+          for (int i = 0; i < kCols; i += 2) {
+            // group mode: the accumulator is positive and below 2^23, so its bit pattern read as a float is
+            // the denormal acc * 2^-149 and the FFMA takes it as it is (a conversion instruction runs at a
+            // sixteenth of the rate); two columns go through one packed FFMA
+            if (kGroup) {
+              ffma2(sums[i], sums[i + 1], r[i], r[i + 1], scale);
+            } else {
+              sums[i] = fmaf(static_cast<float>(static_cast<int32_t>(r[i])), scale, sums[i]);
+              sums[i + 1] = fmaf(static_cast<float>(static_cast<int32_t>(r[i + 1])), scale, sums[i + 1]);
+            }
           }
           if (kDump) {
 #pragma unroll
             for (int i = 0; i < kCols; ++i) {
               if (n_ok && i < my_cols) {
                 const int64_t m = tok0 + my_col0 + i;
-                p.acc_dump[(m * p.N + n) * groups + g] = static_cast<int32_t>(r[i]) >> 4;
+                p.acc_dump[(m * p.N + n) * groups + g] = static_cast<int32_t>(r[i] - offset_bits) >> 4;
               }
             }
           }
@@ -441,8 +493,12 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               if (4 * j + e < my_cols) {
-                float y = __fmul_rn(sums[4 * j + e], rs[e]);
-                if (!kGroup) y = __fmul_rn(y, wscale);
+                float y;
+                if (kGroup) {
+                  y = __fmul_rn(__fsub_rn(sums[4 * j + e], offset_sum), __fmul_rn(rs[e], kScaleDown));
+                } else {
+                  y = __fmul_rn(__fmul_rn(sums[4 * j + e], rs[e]), wscale);
+                }
                 if (has_bias) y = __fadd_rn(y, bias);
                 const int64_t m = m0 + 4 * j + e;
                 if (p.gate != nullptr)
@@ -557,6 +613,11 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
     const int cap = TOK / 4 < 16 ? 16 : TOK / 4;
     const int want = ((tok_tile + 63) / 64) * 16;
     p.slice_cols = want < cap ? want : cap;
+    if (a.codes_int4_range) {
+      p.offset_steps = 1; p.offset_word = 0x40404040u; p.offset_bits = 1u << 17;
+    } else {
+      p.offset_steps = 4; p.offset_word = 0x80808080u; p.offset_bits = 1u << 21;
+    }
   }
   p.tok_tiles = static_cast<int>((a.M + tok_tile - 1) / tok_tile);
   p.k_blocks = static_cast<int>((a.K + kBlockK - 1) / kBlockK);

@@ -40,6 +40,7 @@ struct GemmArgs {
   int out_dtype;
   int64_t M, N, K;
   int32_t* acc_dump;
+  bool codes_int4_range = false;  // SQ_CODES_INT4_RANGE was set: every code lies in [-8, 7]
   // fused epilogue: out = residual + gate * act(acc * scales + bias)
   int activation = SQ_ACT_FN_NONE;
   const void* gate = nullptr;      // rows of N in out's dtype, one per gate_span output rows

@@ -53,9 +53,10 @@ def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None,
 
 def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_scales: torch.Tensor, bias,
          *, out_dtype: torch.dtype, codes_layout: int = _lib.CODES_EVEN_ODD, want_accumulators: bool = False,
-         check_kernel: bool = False, out: torch.Tensor | None = None):
+         check_kernel: bool = False, out: torch.Tensor | None = None, int4_range: bool = False):
     """codes int8 [M, K] x packed uint8 [N, K/2] -> [M, N] in ``out_dtype``.
     ``w_scales`` fp32 [N] selects the per-channel form, fp16 [N, K/128] the group form.
+    ``int4_range`` promises that every code lies in [-8, 7] (SQ_CODES_INT4_RANGE): faster group form.
     ``check_kernel`` runs the CUDA-core cross-check kernel instead of the tensor-core one (tests only)."""
     _require_cuda(codes, "codes")
     m, k = codes.shape
@@ -69,7 +70,7 @@ def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_
     lib = _lib.load_library()
     fn = lib.sq_gemm_check if check_kernel else lib.sq_gemm
     with torch.cuda.device(codes.device):
-        status = fn(codes.data_ptr(), int(codes_layout), packed.data_ptr(), w_scales.data_ptr(),
+        status = fn(codes.data_ptr(), int(codes_layout) | (_lib.CODES_INT4_RANGE if int4_range else 0), packed.data_ptr(), w_scales.data_ptr(),
                     _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32, row_scales.data_ptr(), _ptr(bias),
                     out.data_ptr(), _DTYPES[out_dtype], m, n, k, _ptr(acc), _stream())
     _lib.check(status, "sq_gemm_check" if check_kernel else "sq_gemm")

@@ -44,6 +44,10 @@ extern "C" {
 /* order of the codes along K inside each run of 8 */
 #define SQ_CODES_NATURAL 0 /* k, k+1, ..., k+7                                                     */
 #define SQ_CODES_EVEN_ODD 1 /* k, k+2, k+4, k+6, k+1, k+3, k+5, k+7 (what sq_gemm unpacks fastest) */
+/* sq_gemm only, OR-ed onto the layout: a promise that every code lies in [-8, 7] (what sq_prepass writes for
+ * abits = 4).  The group-scale kernel then starts each accumulator at 2^17 instead of 2^21, which is faster and
+ * loses less fp32 precision; codes outside the range under this promise give wrong sums. */
+#define SQ_CODES_INT4_RANGE 2
 
 /* normalisation fused in front of the quantizer (sq_linear_fused) */
 #define SQ_NORM_NONE 0
@@ -101,14 +105,17 @@ int sq_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, i
  *   out          [M, N] bf16/fp16 (out_dtype), row-major
  *   acc_dump     null, or int32 [M, N, G] (G = 1 or K/128): the exact integer accumulators, for parity checks
  * channel form:  out = dtype((float(acc) * row_scale[m]) * w_scale[n] + bias[n])      (w4a8.cu:324-360)
- * group form:    out = dtype((sum_g float(acc_g) * w_scale[n,g]) * row_scale[m] + bias[n])
+ * group form:    out = dtype((sum_g float(acc_g) * w_scale[n,g]) * row_scale[m] + bias[n]); the sum over groups
+ *                is kept in fp32 in the kernel's own order, so outputs match sq_gemm_check to fp32 rounding
+ *                (about 1e-4 relative before the cast) while the integer accumulators match bit for bit
  * Alignment: K % 32 == 0 (K % 128 == 0 in group form), N % 8 == 0, all pointers 16-byte aligned.
  */
 int sq_gemm(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
             const float* row_scales, const void* bias, void* out, int out_dtype,
             int64_t M, int64_t N, int64_t K, int32_t* acc_dump, void* stream);
 
-/* Plain-CUDA-core version of sq_gemm with the same arguments and the same results.  It exists so the
+/* Plain-CUDA-core version of sq_gemm with the same arguments (SQ_CODES_INT4_RANGE is accepted and ignored), the
+ * same accumulators and, in the group form, the oracle's own fp32 summation order.  It exists so the
  * tensor-core kernel can be cross-checked on the device; it is not a fallback and nothing dispatches to it. */
 int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
                   const float* row_scales, const void* bias, void* out, int out_dtype,

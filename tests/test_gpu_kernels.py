@@ -133,11 +133,42 @@ def test_gemm_group_scheme(native, oracle, m, k, n, abits):
                                codes_layout=layout, want_accumulators=True)
         assert torch.equal(acc.cpu().long(), want["acc"])
         assert rel_fro(out.cpu(), want_out) < 1e-2
-        # same numbers up to the fused multiply-add in the drain: within one bf16 step almost everywhere
+        # same numbers up to the fp32 summation order of the drain: within one bf16 step almost everywhere
         assert rel_fro(out.cpu(), want_out) < 2e-3
         plain = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
                             codes_layout=layout)
         assert torch.equal(plain, out)
+        if abits == 4:  # the promise "codes within [-8, 7]" selects the small accumulator offset
+            out4, acc4 = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
+                                     codes_layout=layout, want_accumulators=True, int4_range=True)
+            assert torch.equal(acc4.cpu().long(), want["acc"])
+            assert rel_fro(out4.cpu(), want_out) < 2e-3
+
+
+@pytest.mark.parametrize("code,weight,int4_range", [(-128, -8, False), (127, -8, False), (-128, 7, False),
+                                                    (127, 7, False), (-8, -8, True), (7, -8, True), (-8, 7, True)])
+def test_gemm_group_extreme_sums(native, oracle, code, weight, int4_range):
+    """Every product of a 128-K group at the same extreme: the largest sums the integer path can meet."""
+    m, k, n = 144, 384, 136
+    gen = torch.Generator().manual_seed(7)
+    codes = torch.full((m, k), code, dtype=torch.int8)
+    qweight = torch.full((n, k), weight, dtype=torch.int8)
+    # a few random rows so the case is not rank one
+    codes[::5] = torch.randint(-8 if int4_range else -128, 8 if int4_range else 128, codes[::5].shape, generator=gen,
+                               dtype=torch.int8)
+    qweight[::3] = torch.randint(-8, 8, qweight[::3].shape, generator=gen, dtype=torch.int8)
+    wscales = (torch.rand(n, k // 128, generator=gen) * 0.01 + 0.001).half()
+    row_scales = torch.rand(m, generator=gen) + 0.5
+    want_acc = torch.einsum("mgk,ngk->mng", codes.view(m, -1, 128).long(), qweight.view(n, -1, 128).long())
+    want_out = oracle.epilogue_group(want_acc, wscales, row_scales, None, torch.bfloat16)
+    packed = oracle.pack_signed_int4(qweight).cuda()
+    out, acc = native.gemm(codes.cuda(), packed, wscales.cuda(), row_scales.cuda(), None, out_dtype=torch.bfloat16,
+                           codes_layout=0, want_accumulators=True, int4_range=int4_range)
+    assert torch.equal(acc.cpu().long(), want_acc)
+    assert rel_fro(out.cpu(), want_out) < 2e-3
+    plain = native.gemm(codes.cuda(), packed, wscales.cuda(), row_scales.cuda(), None, out_dtype=torch.bfloat16,
+                        codes_layout=0, int4_range=int4_range)
+    assert torch.equal(plain, out)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
