@@ -21,6 +21,9 @@ struct PrepassFusion {
   int64_t mod_span = 1;              // input rows per modulation row
   int64_t mod_row_stride = 0;        // elements between modulation rows
   int round_after = 0;               // round the result to x's dtype before rotation / quantization
+  // composite rotation: K = mix_order x (power of two); replaces the block rotation, excludes the fusions above
+  const float* mix = nullptr;        // [mix_order, mix_order] of +-1
+  int mix_order = 0;
 };
 
 int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,

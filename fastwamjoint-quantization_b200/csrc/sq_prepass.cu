@@ -94,6 +94,12 @@ struct PrepassParams {
   const void* mod_shift;
   int64_t mod_span, mod_row_stride;
   int round_after;
+  // composite rotation (kMix): K = mix_order x part, part a power of two in [8, 512]
+  const float* mix;      // [mix_order, mix_order] entries +-1, row-major
+  int mix_order;
+  int mix_part_log2;
+  float mix_part_norm;   // float(1 / sqrt(part))
+  float mix_order_root;  // float(sqrt(mix_order))
 };
 
 constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23
@@ -104,7 +110,9 @@ __device__ __forceinline__ uint32_t round_code(float q, float qmax) {
 }
 
 // kFused compiles the normalisation / modulation front end in; the plain pre-pass keeps its register count.
-template <typename T, int VPT, bool kFused>
+// kMix compiles the composite rotation in (a sign matrix across power-of-two parts of the row, through
+// dynamic shared memory: one fp32 row per row of the CTA, then the matrix).
+template <typename T, int VPT, bool kFused, bool kMix = false>
 __global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) {
   const int tpr = 1 << p.tpr_log2;
   const int t = threadIdx.x & (tpr - 1);
@@ -227,20 +235,100 @@ __global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) 
         }
       }
       // strides 8, 16, ... across lanes: the lane whose bit is clear holds "left"
-      for (int stage = 0; stage < p.rht_lanes_log2; ++stage) {
-        const int lane_bit = 1 << stage;
-        const float mine = (threadIdx.x & lane_bit) != 0 ? -1.0f : 1.0f;  // right: other - v, left: v + other
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float other = __shfl_xor_sync(0xffffffffu, v[j][i], lane_bit);
-          v[j][i] = fmaf(v[j][i], mine, other);
+      for (int stage = 0; stage < 5; ++stage) {  // blocks of up to 256 = 32 lanes x 8
+        if (stage < p.rht_lanes_log2) {
+          constexpr int kOne = 1;
+          const int lane_bit = kOne << stage;
+          const float mine = (threadIdx.x & lane_bit) != 0 ? -1.0f : 1.0f;  // right: other - v, left: v + other
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j][i], lane_bit);
+            v[j][i] = fmaf(v[j][i], mine, other);
+          }
         }
       }
+      if (!kMix) {
 #pragma unroll
-      for (int i = 0; i < 8; i += 2) {
-        v[j][i] = __fmul_rn(v[j][i], p.rht_norm);
-        v[j][i + 1] = __fmul_rn(v[j][i + 1], p.rht_norm);
-        Vec8<T>::round_trip2(v[j][i], v[j][i + 1]);
+        for (int i = 0; i < 8; i += 2) {
+          v[j][i] = __fmul_rn(v[j][i], p.rht_norm);
+          v[j][i + 1] = __fmul_rn(v[j][i + 1], p.rht_norm);
+          Vec8<T>::round_trip2(v[j][i], v[j][i + 1]);
+        }
+      }
+    }
+  }
+
+  if (kMix) {
+    // Composite rotation, the reference's order of operations (rht.py:27-39): normalised FWHT of every part
+    // (the stages up to 256 are done above; a 512-long part needs one more, across warps), then the sign
+    // matrix across the parts, then one division by sqrt(order); rounded to the input type at the end.
+    extern __shared__ __align__(16) float mix_smem[];
+    const int order = p.mix_order;
+    float* matrix = mix_smem;                                   // [order * order], padded to 1024 floats
+    float* buf = mix_smem + 1024 + (threadIdx.x >> p.tpr_log2) * p.K;  // this row, fp32
+    for (int i = threadIdx.x; i < order * order; i += blockDim.x) matrix[i] = __ldg(p.mix + i);
+    const int part = 1 << p.mix_part_log2;
+    if (part == 512) {
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int vec = j * tpr + t;
+        if (vec < vectors) {
+          *reinterpret_cast<float4*>(buf + 8 * vec) = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+          *reinterpret_cast<float4*>(buf + 8 * vec + 4) = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int vec = j * tpr + t;
+        if (vec < vectors) {
+          const int pos = 8 * vec;
+          const float4 o0 = *reinterpret_cast<const float4*>(buf + (pos ^ 256));
+          const float4 o1 = *reinterpret_cast<const float4*>(buf + (pos ^ 256) + 4);
+          const float other[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+          const float mine = (pos & 256) != 0 ? -1.0f : 1.0f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[j][i] = fmaf(v[j][i], mine, other[i]);
+        }
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int vec = j * tpr + t;
+      if (vec < vectors) {
+        float h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = __fmul_rn(v[j][i], p.mix_part_norm);
+        *reinterpret_cast<float4*>(buf + 8 * vec) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(buf + 8 * vec + 4) = make_float4(h[4], h[5], h[6], h[7]);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int vec = j * tpr + t;
+      if (vec < vectors) {
+        const int pos = 8 * vec;
+        const int out_part = pos >> p.mix_part_log2;
+        const int column = pos & (part - 1);
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        for (int src = 0; src < order; ++src) {
+          const float m = matrix[out_part * order + src];
+          const float4 h0 = *reinterpret_cast<const float4*>(buf + (src << p.mix_part_log2) + column);
+          const float4 h1 = *reinterpret_cast<const float4*>(buf + (src << p.mix_part_log2) + column + 4);
+          acc[0] = fmaf(m, h0.x, acc[0]); acc[1] = fmaf(m, h0.y, acc[1]);
+          acc[2] = fmaf(m, h0.z, acc[2]); acc[3] = fmaf(m, h0.w, acc[3]);
+          acc[4] = fmaf(m, h1.x, acc[4]); acc[5] = fmaf(m, h1.y, acc[5]);
+          acc[6] = fmaf(m, h1.z, acc[6]); acc[7] = fmaf(m, h1.w, acc[7]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          v[j][i] = __fdiv_rn(acc[i], p.mix_order_root);
+          v[j][i + 1] = __fdiv_rn(acc[i + 1], p.mix_order_root);
+          Vec8<T>::round_trip2(v[j][i], v[j][i + 1]);
+        }
       }
     }
   }
@@ -310,7 +398,8 @@ __global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) 
         const float q0 = __fmul_rn(x, reciprocal);
         const float q1 = fmaf(fmaf(-q0, divisor, x), reciprocal, q0);
         const float q2 = fmaf(fmaf(-q1, divisor, x), reciprocal, q1);
-        q[i] = round_code(q2, qmax);
+        // no clamp: |x| <= amax and divisor >= RN(amax / qmax) give |q2| <= qmax (1 + 2^-23), which rounds to qmax
+        q[i] = __float_as_uint(__fadd_rn(q2, kRoundMagic));
       }
     } else {
 #pragma unroll
@@ -351,6 +440,29 @@ static cudaError_t launch_for_type(const PrepassParams& p, int vpt, dim3 grid, d
   return cudaGetLastError();
 }
 
+// Composite-rotation instantiations need dynamic shared memory, above the default limit for wide rows.
+template <typename T, int VPT>
+static cudaError_t launch_mix_one(const PrepassParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+  auto kernel = sq_prepass_kernel<T, VPT, false, true>;
+  if (smem > 48 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return err;
+  }
+  kernel<<<grid, block, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t launch_mix(const PrepassParams& p, int vpt, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+  switch (vpt) {
+    case 1: return launch_mix_one<T, 1>(p, grid, block, smem, stream);
+    case 2: return launch_mix_one<T, 2>(p, grid, block, smem, stream);
+    case 3: return launch_mix_one<T, 3>(p, grid, block, smem, stream);
+    case 4: return launch_mix_one<T, 4>(p, grid, block, smem, stream);
+    default: return cudaErrorInvalidValue;  // rows wider than 16384 are rejected before the launch
+  }
+}
+
 int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
                    const float* signs, int rht_block, const float* act_scale, const float* gains, int64_t span,
                    int64_t streams, int64_t seq_tokens, int codes_layout, int pack_int4, void* codes,
@@ -373,7 +485,18 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
   if (rows > (int64_t{1} << 31) - 1) return SQ_ERR_SHAPE;
   int lanes_log2 = 0;
   float norm = 1.0f;
-  if (signs != nullptr) {
+  int part_log2 = 0;
+  if (f.mix != nullptr) {
+    // K = order x part: FWHT of length part (in-warp stages up to 256, one shared-memory stage for 512), then the matrix
+    if (signs == nullptr) return SQ_ERR_NULL;
+    if (f.norm_kind != SQ_NORM_NONE || f.input_activation != SQ_ACT_FN_NONE) return SQ_ERR_ENUM;
+    if (f.mix_order < 2 || f.mix_order > 32 || K % f.mix_order != 0 || K > 16384) return SQ_ERR_SHAPE;
+    const int64_t part = K / f.mix_order;
+    if (part < 8 || part > 512 || (part & (part - 1)) != 0) return SQ_ERR_SHAPE;
+    while ((int64_t{1} << part_log2) < part) ++part_log2;
+    const int64_t in_warp = part < 256 ? part : 256;
+    while ((8 << lanes_log2) < in_warp) ++lanes_log2;
+  } else if (signs != nullptr) {
     if (rht_block < 8 || rht_block > 256 || (rht_block & (rht_block - 1)) != 0 || K % rht_block != 0) return SQ_ERR_SHAPE;
     while ((8 << lanes_log2) < rht_block) ++lanes_log2;
     norm = static_cast<float>(1.0 / std::sqrt(static_cast<double>(rht_block)));
@@ -403,11 +526,18 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
   p.norm_kind = f.norm_kind; p.norm_eps = f.norm_eps; p.norm_weight = f.norm_weight;
   p.mod_scale = f.mod_scale; p.mod_shift = f.mod_shift;
   p.mod_span = f.mod_span > 0 ? f.mod_span : 1; p.mod_row_stride = f.mod_row_stride; p.round_after = f.round_after;
+  p.mix = f.mix; p.mix_order = f.mix_order; p.mix_part_log2 = part_log2;
+  p.mix_part_norm = static_cast<float>(1.0 / std::sqrt(static_cast<double>(int64_t{1} << part_log2)));
+  p.mix_order_root = static_cast<float>(std::sqrt(static_cast<double>(f.mix_order > 0 ? f.mix_order : 1)));
 
   const dim3 grid(static_cast<unsigned>((rows + rows_per_cta - 1) / rows_per_cta));
   const dim3 block(threads);
   cudaError_t err;
-  if (f.norm_kind != SQ_NORM_NONE || f.input_activation != SQ_ACT_FN_NONE) {
+  if (f.mix != nullptr) {
+    const size_t smem = (1024 + static_cast<size_t>(rows_per_cta) * static_cast<size_t>(K)) * sizeof(float);
+    err = x_dtype == SQ_BF16 ? launch_mix<__nv_bfloat16>(p, vpt, grid, block, smem, stream)
+                             : launch_mix<__half>(p, vpt, grid, block, smem, stream);
+  } else if (f.norm_kind != SQ_NORM_NONE || f.input_activation != SQ_ACT_FN_NONE) {
     err = x_dtype == SQ_BF16 ? launch_for_type<__nv_bfloat16, true>(p, vpt, grid, block, stream)
                              : launch_for_type<__half, true>(p, vpt, grid, block, stream);
   } else {

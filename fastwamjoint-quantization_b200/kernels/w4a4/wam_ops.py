@@ -30,11 +30,16 @@ def symmetric_scheduled_stream_linear(x, packed, scales, bias, inverse, activati
 
 
 def symmetric_scheduled_stream_rht_linear(x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
-                                          call, signs, *, rht_block: int = GROUP):
+                                          call, signs, *, rht_block: int = GROUP, mix=None):
     """Rotate, scale, quantize to int4, multiply (``wam_ops.py:56-75``).  The rotation is the block-local
-    power-of-two Hadamard transform of length ``rht_block``."""
+    power-of-two Hadamard transform of length ``rht_block``, or - with ``mix``, an fp32 ``[order, order]`` sign
+    matrix - the reference's composite rotation ``order x power of two`` (had12 x H256 at K = 3072, had28 x H512
+    at K = 14336, ``rht.py:27-39``)."""
     x = _common(x, packed, scales, bias, inverse)
     span = stream_span(x, gains, token_counts, activation_scales, strict_positive=True)
+    if mix is not None:
+        return scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, abits=4,
+                                signs=_check_signs(x, signs), mix=mix)
     return scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, abits=4,
                             signs=_check_signs(x, signs), rht_block=rht_block)
 

@@ -26,10 +26,11 @@ def _stream():
 
 def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None, rht_block: int = 128,
             act_scale=None, gains=None, span: int = 1, streams: int = 1, seq_tokens: int | None = None,
-            codes_layout: int = _lib.CODES_EVEN_ODD, pack_int4: bool = False, out=None):
+            codes_layout: int = _lib.CODES_EVEN_ODD, pack_int4: bool = False, out=None, mix=None):
     """Run the fused activation pre-pass.  ``x`` is [..., tokens, K] bf16/fp16.
     Returns ``(codes, row_scales)``: int8 [rows, K] (or uint8 [rows, K/2] when
-    ``pack_int4``) and fp32 [rows]."""
+    ``pack_int4``) and fp32 [rows].  ``mix`` (fp32 [order, order] of +-1) selects the composite rotation
+    ``order x power of two`` instead of the block rotation of length ``rht_block``."""
     _require_cuda(x, "x")
     x = x.contiguous()
     k = x.shape[-1]
@@ -40,6 +41,17 @@ def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None,
         codes = torch.empty((rows, k // 2) if pack_int4 else (rows, k), device=x.device,
                             dtype=torch.uint8 if pack_int4 else torch.int8)
         row_scales = torch.empty((rows,), device=x.device, dtype=torch.float32)
+    if mix is not None:
+        mix = _mix_matrix(mix, x)
+        with torch.cuda.device(x.device):
+            status = _lib.load_library().sq_prepass_composite(
+                x.data_ptr(), _DTYPES[x.dtype], rows, k, int(abits),
+                _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
+                _ptr(inverse), _ptr(signs), mix.data_ptr(), int(mix.shape[0]), _ptr(act_scale), _ptr(gains),
+                int(span), int(streams), int(seq_tokens if seq_tokens is not None else x.shape[-2]),
+                int(codes_layout), int(bool(pack_int4)), codes.data_ptr(), row_scales.data_ptr(), _stream())
+        _lib.check(status, "sq_prepass_composite")
+        return codes, row_scales
     with torch.cuda.device(x.device):
         status = _lib.load_library().sq_prepass(
             x.data_ptr(), _DTYPES[x.dtype], rows, k, int(abits),
@@ -49,6 +61,12 @@ def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None,
             int(codes_layout), int(bool(pack_int4)), codes.data_ptr(), row_scales.data_ptr(), _stream())
     _lib.check(status, "sq_prepass")
     return codes, row_scales
+
+
+def _mix_matrix(mix: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    if mix.ndim != 2 or mix.shape[0] != mix.shape[1] or mix.dtype != torch.float32 or mix.device != x.device:
+        raise ValueError("mix must be a square fp32 matrix on the input's device.")
+    return mix.contiguous()
 
 
 def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_scales: torch.Tensor, bias,
@@ -93,7 +111,7 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
            span: int = 1, streams: int = 1, out: torch.Tensor | None = None,
            workspace: torch.Tensor | None = None, norm: str | None = None, norm_eps: float = 1e-6, norm_weight=None,
            mod_scale=None, mod_shift=None, round_after_norm: bool = False, activation: str | None = None,
-           gate=None, residual=None, input_activation: str | None = None) -> torch.Tensor:
+           gate=None, residual=None, input_activation: str | None = None, mix=None) -> torch.Tensor:
     """One whole quantized linear (pre-pass + GEMM) through ``sq_linear_fused``.  ``out`` and ``workspace``
     (uint8, at least ``sq_workspace_bytes(rows, K)``) may be passed to reuse buffers across calls.
 
@@ -119,6 +137,22 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
         raise RuntimeError("out must be a contiguous tensor of shape x.shape[:-1] + (N,) in x's dtype.")
     group = w_scales.dtype == torch.float16
     calls = 0 if act_scales is None else act_scales.numel()
+    if mix is not None:
+        # composite rotation (order x power of two); a rotated site takes no block fusion (runtime.py:75-78)
+        if (norm is not None or mod_scale is not None or gate is not None or residual is not None
+                or activation is not None or input_activation is not None):
+            raise ValueError("the composite rotation cannot be combined with fused block work.")
+        mix = _mix_matrix(mix, x)
+        with torch.cuda.device(x.device):
+            status = lib.sq_linear_composite(
+                x.data_ptr(), _DTYPES[x.dtype], rows, k, n, int(abits),
+                _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
+                _ptr(inverse), _ptr(signs), mix.data_ptr(), int(mix.shape[0]), _ptr(act_scales), _ptr(gains),
+                int(calls), int(call), int(span), int(streams), int(x.shape[-2]),
+                packed.data_ptr(), w_scales.data_ptr(), _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32,
+                _ptr(bias), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
+        _lib.check(status, "sq_linear_composite")
+        return out
     norm_kind = {None: _lib.NORM_NONE, "layer": _lib.NORM_LAYER, "rms": _lib.NORM_RMS}[norm]
     mod_ptr = shift_ptr = gate_ptr = None
     mod_span = gate_span = 1

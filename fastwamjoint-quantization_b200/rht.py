@@ -62,6 +62,35 @@ def randomized_block_hadamard_transform(values: torch.Tensor, signs: torch.Tenso
     return block_hadamard(values * signs.to(device=values.device, dtype=values.dtype), block)
 
 
+def composite_order(width: int) -> int | None:
+    """Order of the sign matrix the reference's "rht" rotation uses for this width (``rht.py:31-34``):
+    12 at 3072, 28 at 14336, none for powers of two (plain FWHT)."""
+    return {3072: 12, 14336: 28}.get(int(width))
+
+
+def composite_hadamard(values: torch.Tensor, matrix: torch.Tensor) -> torch.Tensor:
+    """``rht.py:27-39`` with the sign matrix as an argument: view the last axis as ``[order, P]`` (P a power of
+    two), normalised FWHT of every row, the matrix across the rows, one division by ``sqrt(order)``.  The
+    order-12 / order-28 matrices belong to the checkpoint's tooling and are passed in by the caller."""
+    order = int(matrix.shape[0])
+    width = int(values.shape[-1])
+    if matrix.ndim != 2 or matrix.shape[1] != order or width % order:
+        raise ValueError("matrix must be square and its order must divide the width.")
+    part = width // order
+    if part & (part - 1):
+        raise ValueError("width / order must be a power of two.")
+    transformed = block_hadamard(values.float().reshape(-1, order, part), part)
+    mixed = matrix.to(device=values.device, dtype=torch.float32) @ transformed
+    return mixed.reshape(values.shape) / torch.full((), math.sqrt(order), device=values.device)
+
+
+def randomized_composite_hadamard_transform(values: torch.Tensor, signs: torch.Tensor, matrix: torch.Tensor):
+    """``composite_hadamard(values * signs)`` (``rht.py:45-46, 56-59``)."""
+    if values.ndim == 0 or tuple(signs.shape) != (values.shape[-1],):
+        raise ValueError("Official RHT requires one sign per input channel.")
+    return composite_hadamard(values * signs.to(device=values.device, dtype=values.dtype), matrix)
+
+
 def rotate_weight_(weight: torch.Tensor, signs: torch.Tensor, block: int = RHT_BLOCK, rows_per_step: int = 128):
     """Rotate a Linear weight in place along its input axis: fp32 rotate, round back to the weight's dtype
     (``rht_install.py:39-41``), in row chunks so no second fp32 copy of a wide matrix exists."""

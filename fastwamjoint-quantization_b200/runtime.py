@@ -12,10 +12,12 @@ Native buffers follow the deployment conventions (``runtime.py:88-92``, ``deploy
 ``weight`` packed uint8 [N, K/2], ``weight_scales`` fp32 [N], ``input_scale`` = 1/D, ``clipping_ranges`` =
 clip / qmax, ``gamma_gains`` [calls, streams], optional ``input_rotation_signs`` fp32 [K].
 
-Rotated sites: the reference's production rotation for K = 3072 / 14336 is a full-width composite
-transform; the kernels here implement the block-local power-of-two rotation (``rotation_block``, the
-largest power of two dividing K capped at 256, or whatever the caller sets).  Both backends of this
-class use the same block, so they agree with each other.
+Rotated sites: by default the rotation is block-local (``rotation_block``, the largest power of two
+dividing K capped at 256, or whatever the caller sets).  The reference's production rotation for
+K = 3072 / 14336 is the composite ``had12 x H256`` / ``had28 x H512`` (``rht.py:27-39``); it is selected by
+passing that order's sign matrix as ``rotation_matrix`` (the matrices belong to the checkpoint's tooling and
+are not part of this package).  Both backends of this class use the same rotation, so they agree with each
+other.
 """
 from __future__ import annotations
 
@@ -27,13 +29,14 @@ import torch.nn.functional as F
 
 from .checkpoint import QuantizedSite
 from .quant import symmetric_fake_quant
-from .rht import randomized_block_hadamard_transform, rht_block_size
+from .rht import randomized_block_hadamard_transform, randomized_composite_hadamard_transform, rht_block_size
 from .state import DenoiseCallState
 from .streams import FastWAMStreamConfig, expand_stream_gains, resolve_stream_layout
 from .topology import LinearSite, resolve_site_module, resolve_site_parent, stream_kind_of
 
 BACKENDS = ("reference", "cutlass_w4a8", "cutlass_w4a4")
 _BUFFERS = ("weight", "weight_scales", "input_scale", "gamma_gains", "clipping_ranges", "bias", "input_rotation_signs")
+# "rotation_matrix" is an optional extra buffer of rotated sites (see the module docstring)
 
 
 def default_rotation_block(width: int) -> int:
@@ -74,6 +77,7 @@ class WAMQuantLinear(nn.Module):
         for name in _BUFFERS:
             self.register_buffer(name, tensors.get(name))
         self.rotation_block = int(spec.get("rotation_block", default_rotation_block(self.weight.shape[1] * 2)))
+        self.register_buffer("rotation_matrix", tensors.get("rotation_matrix"))
         self.site = LinearSite(spec["site_index"], spec["expert"], -1, spec["operation"], spec["module_name"], None,
                                stream_kind_of(spec["operation"]))
         return self
@@ -81,7 +85,8 @@ class WAMQuantLinear(nn.Module):
     def __init__(self, source: nn.Linear, entry: QuantizedSite, *, state: DenoiseCallState,
                  stream_config: FastWAMStreamConfig, weight_bits: int, activation_bits: int,
                  backend: Literal["reference", "cutlass_w4a8", "cutlass_w4a4"] = "reference",
-                 fuse_block: bool = False, rotation_block: int | None = None) -> None:
+                 fuse_block: bool = False, rotation_block: int | None = None,
+                 rotation_matrix: torch.Tensor | None = None) -> None:
         super().__init__()
         entry.validate(state.num_calls)
         if backend not in BACKENDS:
@@ -100,6 +105,16 @@ class WAMQuantLinear(nn.Module):
         self.rotation_block = int(rotation_block or default_rotation_block(entry.qweight.shape[1]))
         signs = entry.input_rotation_signs
         self.register_buffer("input_rotation_signs", None if signs is None else signs.float().to(device))
+        if rotation_matrix is not None:
+            order = int(rotation_matrix.shape[0])
+            width = int(entry.qweight.shape[1])
+            part = width // order if order > 0 and width % order == 0 else 0
+            if (not rotated or rotation_matrix.ndim != 2 or rotation_matrix.shape[1] != order or part < 8
+                    or part > 512 or part & (part - 1)):
+                raise ValueError("rotation_matrix must be a square sign matrix whose order times a power of two "
+                                 "(8..512) is the input width of a rotated site.")
+            rotation_matrix = rotation_matrix.float().to(device)
+        self.register_buffer("rotation_matrix", rotation_matrix)
         if native:
             ops = _native_ops(activation_bits)
             self._native_ops = ops
@@ -151,13 +166,15 @@ class WAMQuantLinear(nn.Module):
                     self.gamma_gains, layout.token_counts, call)
             if self.input_rotation_signs is not None:
                 return self._native_ops.symmetric_scheduled_stream_rht_linear(
-                    *args, self.input_rotation_signs, rht_block=self.rotation_block)
+                    *args, self.input_rotation_signs, rht_block=self.rotation_block, mix=self.rotation_matrix)
             return self._native_ops.symmetric_scheduled_stream_linear(*args)
         return self._reference_forward(x, call, layout)
 
     def _reference_forward(self, x, call, layout):
         """Fake-quant forward of the reference (``runtime.py:155-175``), dividing order."""
-        if self.input_rotation_signs is not None:
+        if self.input_rotation_signs is not None and self.rotation_matrix is not None:
+            x = randomized_composite_hadamard_transform(x.float(), self.input_rotation_signs, self.rotation_matrix).to(x.dtype)
+        elif self.input_rotation_signs is not None:
             x = randomized_block_hadamard_transform(x.float(), self.input_rotation_signs, self.rotation_block).to(x.dtype)
         gains = self.gamma_gains[call].to(device=x.device, dtype=torch.float32)
         if gains.numel() != layout.num_streams:

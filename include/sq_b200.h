@@ -145,6 +145,24 @@ int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, in
               const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
               void* out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The composite rotation of widths K = order x part with part a power of two in [8, 512]: the reference's
+ * had12 x H256 at K = 3072 and had28 x H512 at K = 14336 (rht.py:27-39; device producer rht.cuh:8-100).
+ * Per row: multiply by `signs`, normalised FWHT of every `part` consecutive elements, then
+ * out[i * part + c] = (sum_j mix[i, j] * h[j * part + c]) / sqrt(order), rounded to x_dtype; the rest is
+ * sq_prepass / sq_linear.  `mix` is float [order, order] with entries +-1 (the caller's Hadamard matrix of that
+ * order, device memory), 2 <= order <= 32, K <= 16384.  The sum over j runs in ascending j in fp32, which is
+ * not the reference's BLAS order: rotated values agree to fp32 rounding, codes to +-1 on a few in ten thousand. */
+int sq_prepass_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
+                         const float* signs, const float* mix, int mix_order, const float* act_scale,
+                         const float* gains, int64_t span, int64_t streams, int64_t seq_tokens, int codes_layout,
+                         int pack_int4, void* codes, float* row_scales, void* stream);
+int sq_linear_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+                        const float* inv_d, const float* signs, const float* mix, int mix_order,
+                        const float* act_scales, const float* gains, int64_t calls, int64_t call, int64_t span,
+                        int64_t streams, int64_t seq_tokens, const void* w_packed, const void* w_scales,
+                        int wscale_mode, const void* bias, void* out, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
 /* sq_linear with work of the surrounding block folded into its two kernels.
  * Pre-pass side, replaces quantize_static_adaln_stream_kernel / quantize_dynamic_adaln_per_token_kernel
  * (w4a8.cu:519-691) and their int4 forms (w4a4.cu:963-1049, 1126-1211): optionally an activation of the input

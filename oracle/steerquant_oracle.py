@@ -134,6 +134,28 @@ def rht_rotate(values: torch.Tensor, signs: torch.Tensor, block: int = RHT_BLOCK
     return block_hadamard(values.float() * signs.float(), block)
 
 
+def composite_hadamard(values: torch.Tensor, matrix: torch.Tensor) -> torch.Tensor:
+    """The rotation of widths that are ``order x power of two`` (3072 = 12 x 256, 14336 = 28 x 512), following
+    ``rht.py:27-39``: view the last axis as ``[order, P]``, normalised FWHT of length P on every row, then the
+    ``order x order`` sign matrix applied across the rows, then one division by ``sqrt(order)``.  The reference
+    rebuilds its order-12 / order-28 matrices from pinned masks (``rht.py:18-24``); here the matrix is an argument."""
+    order = int(matrix.shape[0])
+    width = int(values.shape[-1])
+    if matrix.shape != (order, order) or width % order:
+        raise ValueError("matrix must be square and its order must divide the width.")
+    part = width // order
+    if part & (part - 1):
+        raise ValueError("width / order must be a power of two.")
+    blocks = values.float().reshape(-1, order, part)
+    transformed = block_hadamard(blocks, part)
+    return (matrix.float() @ transformed).reshape(values.shape) / math.sqrt(order)
+
+
+def composite_rotate(values: torch.Tensor, signs: torch.Tensor, matrix: torch.Tensor) -> torch.Tensor:
+    """``composite_hadamard(values * signs)`` in fp32 (``rht.py:45-46``)."""
+    return composite_hadamard(values.float() * signs.float(), matrix)
+
+
 def rotate_weight(weight: torch.Tensor, signs: torch.Tensor, dtype: torch.dtype,
                   block: int = RHT_BLOCK) -> torch.Tensor:
     """Weight-side rotation: fp32 rotate, round to the model dtype

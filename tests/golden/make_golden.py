@@ -122,6 +122,17 @@ def main() -> None:
             if rotated:
                 out[f"mod_{tag}_signs"] = signs.numpy()
 
+    # --- the composite rotation of widths 3072 / 14336 (rht.py:18-39): the order-12 / order-28 sign matrices
+    # the reference rebuilds from its pinned masks, and its transform of seeded rows
+    mix_gen = torch.Generator(device="cpu").manual_seed(4321)
+    for order, width, rows in ((12, 3072, 2), (28, 14336, 1)):
+        out[f"mix{order}_matrix"] = rht.official_hadamard_matrix(order).to(torch.int8).numpy()
+        xin = torch.randn(rows, width, generator=mix_gen) * 1.5
+        signs_w = rht.rht_signs(width, seed=42, module_name="linear")
+        out[f"mix{order}_in"] = xin.numpy()
+        out[f"mix{order}_out"] = rht.rht_transform(xin, signs_w, "rht").numpy()
+        out[f"mix{order}_out_bf16"] = bits(rht.rht_transform(xin.bfloat16().float(), signs_w, "rht").to(torch.bfloat16))
+
     np.savez_compressed(args.out, **out)
     print(f"wrote {args.out}: {len(out)} arrays, {Path(args.out).stat().st_size} bytes")
 

@@ -109,6 +109,50 @@ def test_prepass_static_schedule(native, oracle, dtype, m, k, counts, batch, abi
         assert torch.equal(rows.cpu(), want_rows.repeat(batch))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("order,k,rows", [(12, 3072, 50), (28, 14336, 9), (12, 96, 5), (12, 1536, 33), (28, 7168, 3)])
+@pytest.mark.parametrize("abits,mode", [(4, "token"), (8, "token"), (4, "static")])
+def test_prepass_composite_rotation(native, oracle, golden, dtype, order, k, rows, abits, mode):
+    """Composite rotation order x power-of-two (rht.py:27-39) in the pre-pass.  The matrix sum runs in a
+    different fp32 order than the CPU matmul of the oracle, so a rotated value may land on the other side of a
+    rounding boundary: codes differ by at most 1 on at most 0.1 % of the elements, row scales agree to 1e-6."""
+    gen = torch.Generator().manual_seed(order * k + rows)
+    matrix = golden[f"mix{order}_matrix"].float()
+    x = (torch.randn(rows, k, generator=gen) * 2.0).to(dtype)
+    signs = oracle.rht_signs(k, seed=3, module_name="site")
+    rotated = oracle.composite_rotate(x.float(), signs, matrix).to(dtype)
+    if mode == "token":
+        want_codes, want_rows = oracle.token_codes(rotated, bits=abits)
+        codes, row_scales = native.prepass(x.cuda(), abits=abits, mode="token", signs=signs.cuda(), mix=matrix.cuda(),
+                                           codes_layout=0)
+    else:
+        inverse = torch.pow(2.0, torch.randint(-1, 2, (k,), generator=gen).float())
+        scales = torch.tensor([0.25, 0.5])
+        gains = torch.tensor([[1.0], [2.0]])
+        want_codes, want_rows = oracle.static_codes(rotated.reshape(1, rows, k), bits=abits, inverse=inverse,
+                                                    activation_scales=scales, gains=gains, token_counts=(rows,), call=1)
+        want_codes = want_codes.reshape(rows, k)
+        codes, row_scales = native.prepass(x.cuda(), abits=abits, mode="static", inverse=inverse.cuda(),
+                                           signs=signs.cuda(), mix=matrix.cuda(), act_scale=scales.cuda()[1:],
+                                           gains=gains.cuda()[1], span=rows, streams=1, codes_layout=0)
+    delta = (codes.cpu().int() - want_codes.int()).abs()
+    assert int(delta.max()) <= 1
+    assert float((delta != 0).float().mean()) <= 1e-3
+    torch.testing.assert_close(row_scales.cpu(), want_rows.reshape(-1).float(), rtol=1e-6, atol=0)
+
+
+def test_composite_rotation_rejections(native, golden):
+    matrix = golden["mix12_matrix"].float().cuda()
+    x = torch.zeros(4, 3072, device="cuda", dtype=torch.bfloat16)
+    signs = torch.ones(3072, device="cuda")
+    with pytest.raises(RuntimeError, match="null"):  # a rotation needs its signs
+        native.prepass(x, abits=4, mode="token", mix=matrix)
+    with pytest.raises(RuntimeError, match="shape"):  # 3072 / 28 is not an integer
+        native.prepass(x, abits=4, mode="token", signs=signs, mix=golden["mix28_matrix"].float().cuda())
+    with pytest.raises(ValueError, match="square"):
+        native.prepass(x, abits=4, mode="token", signs=signs, mix=matrix[:6])
+
+
 GEMM_SHAPES = [(256, 1024, 1024), (96, 512, 256), (1, 128, 8), (300, 3072, 384), (17, 256, 136), (520, 1024, 128)]
 
 

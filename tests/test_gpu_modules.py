@@ -154,6 +154,63 @@ def test_rotated_native_module_against_its_reference_backend(m, oracle, k, n, ro
             torch.testing.assert_close(captured, actual, atol=0, rtol=0)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,k,n", [(32, 3072, 1024), (129, 3072, 3072), (294, 3072, 14336), (294, 14336, 3072)])
+def test_official_composite_rotation_module_and_graph(m, oracle, golden, dtype, rows, k, n):
+    """The reference's production rotation (had12 x H256 at 3072, had28 x H512 at 14336) through the module,
+    cases and bars of tests/test_rht.py:101-150: relative RMS < 0.003 against rotate -> round to dtype ->
+    multiply by 1/D and gain/scale -> round, clamp -> integer matmul -> scales, and graph replay bit-equal to
+    eager before and after the input changes."""
+    R = m["runtime"]
+    torch.manual_seed(42)
+    counts = (128, 1) if rows == 129 else (16, 16) if rows == 32 else (98, 98, 98)
+    names = ("text", "proprio") if rows == 129 else tuple(
+        f"action_chunk_{i}" if rows == 32 else f"latent_frame_{i}" for i in range(len(counts)))
+    matrix = golden[f"mix{12 if k == 3072 else 28}_matrix"].float()
+    rht = importlib.import_module(P + "rht")
+    entry = m["checkpoint"].QuantizedSite(
+        0, "linear", "video" if rows == 294 else "action", "cross_attn.k" if rows == 129 else "self_attn.q", names,
+        torch.randint(-7, 8, (n, k), dtype=torch.int8), torch.full((n, 1), 0.002), torch.linspace(0.5, 2, k),
+        torch.ones(10, len(counts)), torch.linspace(2.0, 4.0, 10),
+        torch.tensor(counts).float()[None].repeat(10, 1) / rows, 0.0, 0.0, (0.0,) * 10, (0.0,) * 10,
+        rht.rht_signs(k, seed=42, module_name="linear"), "rht")
+    raw = torch.linspace(-0.4, 0.4, len(counts))
+    entry.gamma_gains[:] = (raw - (raw * entry.token_fractions[0]).sum()).exp()
+    source = torch.nn.Linear(k, n, device="cuda", dtype=dtype)
+    state = m["state"].DenoiseCallState(10)
+    module = R.WAMQuantLinear(source, entry, state=state, stream_config=m["streams"].FastWAMStreamConfig(),
+                              weight_bits=4, activation_bits=4, backend="cutlass_w4a4", rotation_matrix=matrix)
+    x = torch.randn(2 if rows == 129 else 1, rows, k, device="cuda", dtype=dtype)
+
+    def expected(call):
+        z = oracle.composite_rotate(x.cpu().float(), entry.input_rotation_signs, matrix).to(dtype).float()
+        gain = torch.repeat_interleave(entry.gamma_gains[call], torch.tensor(counts))[None, :, None]
+        scale = entry.clipping_ranges[call] / 7
+        codes = (z * entry.input_scale.reciprocal() * (gain / scale)).round().clamp(-7, 7)
+        acc = torch.nn.functional.linear(codes, entry.qweight.float())
+        return (acc * (scale / gain) * entry.weight_scales.reshape(-1) + source.bias.detach().cpu().float()).to(dtype)
+
+    with torch.inference_mode():
+        for call in (0, 9):
+            state.set(call)
+            actual = module(x)
+            want = expected(call)
+            rel = (actual.cpu().float() - want.float()).square().mean().sqrt() / want.float().square().mean().sqrt()
+            assert rel < 0.003, float(rel)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                captured = module(x)
+            graph.replay()
+            torch.testing.assert_close(captured, actual, atol=0, rtol=0)
+            x.mul_(0.79)
+            eager = module(x)
+            graph.replay()
+            torch.testing.assert_close(captured, eager, atol=0, rtol=0)
+    with pytest.raises(ValueError, match="block fusion"):
+        R.WAMQuantLinear(source, entry, state=state, stream_config=m["streams"].FastWAMStreamConfig(), weight_bits=4,
+                         activation_bits=4, backend="cutlass_w4a4", fuse_block=True, rotation_matrix=matrix)
+
+
 class Tiny(torch.nn.Module):
     """Smallest model with the hook points the live-graph glue replaces (tests/test_rollout_graph.py)."""
 

@@ -23,6 +23,20 @@ def test_rotation_wrappers(oracle, golden):
     assert torch.equal(got.view(torch.int16), golden.bf16("rot_bf16_out").view(torch.int16))
 
 
+def test_composite_rotation_3072_and_14336(oracle, golden):
+    """had12 x H256 and had28 x H512 (rht.py:27-39).  The restatement follows the reference operation by
+    operation on the CPU, so it is bit-exact there; the sign matrices are the reference's own."""
+    for order, width in ((12, 3072), (28, 14336)):
+        matrix = golden[f"mix{order}_matrix"]
+        assert matrix.shape == (order, order) and set(matrix.flatten().tolist()) == {-1, 1}
+        assert torch.equal(matrix.long() @ matrix.long().T, order * torch.eye(order, dtype=torch.long))
+        signs = oracle.rht_signs(width, seed=42, module_name="linear")
+        x = golden[f"mix{order}_in"]
+        assert torch.equal(oracle.composite_rotate(x, signs, matrix), golden[f"mix{order}_out"])
+        got = oracle.composite_rotate(x.bfloat16().float(), signs, matrix).to(torch.bfloat16)
+        assert torch.equal(got.view(torch.int16), golden.bf16(f"mix{order}_out").view(torch.int16))
+
+
 def test_fake_quant_and_token_codes(oracle, golden):
     v = golden["fq_in"]
     for bits in (8, 4):
