@@ -110,10 +110,12 @@ __device__ __forceinline__ uint32_t round_code(float q, float qmax) {
 }
 
 // kFused compiles the normalisation / modulation front end in; the plain pre-pass keeps its register count.
+// The plain kernel with up to three vectors per thread fits 48 registers without spills: five 256-thread blocks
+// per SM instead of four.  Every variant stays within 128 registers, so the 512-thread launches fit an SM.
 // kMix compiles the composite rotation in (a sign matrix across power-of-two parts of the row, through
 // dynamic shared memory: one fp32 row per row of the CTA, then the matrix).
 template <typename T, int VPT, bool kFused, bool kMix = false>
-__global__ void __launch_bounds__(512) sq_prepass_kernel(const PrepassParams p) {
+__global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepass_kernel(const PrepassParams p) {
   const int tpr = 1 << p.tpr_log2;
   const int t = threadIdx.x & (tpr - 1);
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> p.tpr_log2) + (threadIdx.x >> p.tpr_log2);
