@@ -43,6 +43,12 @@ _SIGNATURES = {
                                 c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
                                 c_int, c_void_p, c_int64, c_int64, c_void_p,
                                 c_void_p, c_void_p, c_size_t, c_void_p]),
+    "sq_linear_scheduled": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
+                                    c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                    c_void_p, c_void_p, c_int, c_void_p,
+                                    c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int,
+                                    c_int, c_void_p, c_int64, c_int64, c_void_p,
+                                    c_void_p, c_void_p, c_size_t, c_void_p]),
     "sq_prepass_composite": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                      c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p]),

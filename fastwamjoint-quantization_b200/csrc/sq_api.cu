@@ -231,16 +231,39 @@ int sq_linear_fused(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t
                     const void* mod_shift, int64_t mod_span, int64_t mod_row_stride, int round_after_norm,
                     int activation, const void* gate, int64_t gate_span, int64_t gate_row_stride,
                     const void* residual, void* out, void* workspace, size_t workspace_bytes, void* stream) {
+  return sq_linear_scheduled(x, x_dtype, rows, K, N, abits, mode, inv_d, signs, rht_block, act_scales, gains, calls,
+                             call, nullptr, span, streams, seq_tokens, w_packed, w_scales, wscale_mode, bias,
+                             input_activation, norm_kind, norm_eps, norm_weight, mod_scale, mod_shift, mod_span,
+                             mod_row_stride, round_after_norm, activation, gate, gate_span, gate_row_stride, residual,
+                             out, workspace, workspace_bytes, stream);
+}
+
+int sq_linear_scheduled(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+                        const float* inv_d, const float* signs, int rht_block, const float* act_scales,
+                        const float* gains, int64_t calls, int64_t call, const int32_t* call_index, int64_t span,
+                        int64_t streams, int64_t seq_tokens, const void* w_packed, const void* w_scales,
+                        int wscale_mode, const void* bias, int input_activation, int norm_kind, float norm_eps,
+                        const void* norm_weight, const void* mod_scale, const void* mod_shift, int64_t mod_span,
+                        int64_t mod_row_stride, int round_after_norm, int activation, const void* gate,
+                        int64_t gate_span, int64_t gate_row_stride, const void* residual, void* out,
+                        void* workspace, size_t workspace_bytes, void* stream) {
   if (workspace == nullptr && rows > 0) return SQ_ERR_NULL;
   if (workspace_bytes < sq_workspace_bytes(rows, K)) return SQ_ERR_WORKSPACE;
   const float* act_scale = nullptr;
   const float* gain_row = nullptr;
   if (mode == SQ_ACT_STATIC) {
     if (act_scales == nullptr || gains == nullptr) return SQ_ERR_NULL;
-    if (calls <= 0 || call < 0 || call >= calls) return SQ_ERR_INDEX;
     if (streams <= 0) return SQ_ERR_SHAPE;
-    act_scale = act_scales + call;
-    gain_row = gains + call * streams;
+    if (call_index != nullptr) {
+      // the entry is read (and clamped to the table) on the device: the tables are passed whole
+      if (calls <= 0) return SQ_ERR_INDEX;
+      act_scale = act_scales;
+      gain_row = gains;
+    } else {
+      if (calls <= 0 || call < 0 || call >= calls) return SQ_ERR_INDEX;
+      act_scale = act_scales + call;
+      gain_row = gains + call * streams;
+    }
   }
   int8_t* codes = static_cast<int8_t*>(workspace);
   float* row_scales = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
@@ -256,6 +279,10 @@ int sq_linear_fused(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t
   fusion.norm_kind = norm_kind; fusion.norm_eps = norm_eps; fusion.norm_weight = norm_weight;
   fusion.mod_scale = mod_scale; fusion.mod_shift = mod_shift; fusion.mod_span = mod_span;
   fusion.mod_row_stride = mod_row_stride; fusion.round_after = round_after_norm;
+  if (mode == SQ_ACT_STATIC && call_index != nullptr) {
+    fusion.call_index = call_index;
+    fusion.calls = calls;
+  }
   if (rows > 0) {
     int v = sq::validate_gemm(a);
     if (v != SQ_OK) return v;

@@ -117,18 +117,27 @@ __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.al
 template <int kRegs>
 __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs)); }
 
-// (c0, c1) += (a0, a1) * s as one packed single-precision FMA; a0 / a1 are raw bit patterns
-__device__ __forceinline__ void ffma2(float& c0, float& c1, uint32_t a0, uint32_t a1, float s) {
+// Packed single-precision pairs live in 64-bit registers, so the compiler keeps them in aligned register pairs
+// and the packed FMA needs no moves around it.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ float2 unpack2(uint64_t v) {
+  float2 f;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(f.x), "=f"(f.y) : "l"(v));
+  return f;
+}
+// c += (a0, a1) * b as one packed FMA; a0 / a1 are raw bit patterns of two adjacent registers
+__device__ __forceinline__ void ffma2(uint64_t& c, uint32_t a0, uint32_t a1, uint64_t b) {
   asm("{\n\t"
-      ".reg .b64 a, b, c;\n\t"
-      "mov.b64 a, {%2, %3};\n\t"
-      "mov.b64 b, {%4, %4};\n\t"
-      "mov.b64 c, {%0, %1};\n\t"
-      "fma.rn.f32x2 c, a, b, c;\n\t"
-      "mov.b64 {%0, %1}, c;\n\t"
+      ".reg .b64 a;\n\t"
+      "mov.b64 a, {%1, %2};\n\t"
+      "fma.rn.f32x2 %0, a, %3, %0;\n\t"
       "}\n"
-      : "+f"(c0), "+f"(c1)
-      : "r"(a0), "r"(a1), "f"(s));
+      : "+l"(c)
+      : "r"(a0), "r"(a1), "l"(b));
 }
 
 __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_flag, int code) {
@@ -400,9 +409,13 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       const int64_t n = ch0 + ch_in_tile;
       const bool n_ok = n < p.N;
 
-      float sums[kCols];
+      // group form: packed pairs (columns 2i, 2i + 1); channel form: plain floats
+      uint64_t sums2[kGroup ? kCols / 2 : 1];
+      float sums[kGroup ? 1 : kCols];
 #pragma unroll
-      for (int i = 0; i < kCols; ++i) sums[i] = 0.0f;
+      for (int i = 0; i < (kGroup ? kCols / 2 : 1); ++i) sums2[i] = 0ull;
+#pragma unroll
+      for (int i = 0; i < (kGroup ? 1 : kCols); ++i) sums[i] = 0.0f;
       float offset_sum = 0.0f;  // what the constant offsets added to every sum of this channel
 
       // group scales are fetched two groups ahead as raw fp16 bits and converted when used, so the
@@ -442,16 +455,18 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
         if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
         if (my_cols > 0) {
+          const uint64_t scale2 = pack2(scale, scale);
 #pragma unroll
           for (int i = 0; i < kCols; i += 2) {
             // group mode: the accumulator is positive and below 2^23, so its bit pattern read as a float is
             // the denormal acc * 2^-149 and the FFMA takes it as it is (a conversion instruction runs at a
             // sixteenth of the rate); two columns go through one packed FFMA
             if (kGroup) {
-              ffma2(sums[i], sums[i + 1], r[i], r[i + 1], scale);
+              ffma2(sums2[kGroup ? i / 2 : 0], r[i], r[i + 1], scale2);
             } else {
-              sums[i] = fmaf(static_cast<float>(static_cast<int32_t>(r[i])), scale, sums[i]);
-              sums[i + 1] = fmaf(static_cast<float>(static_cast<int32_t>(r[i + 1])), scale, sums[i + 1]);
+              sums[kGroup ? 0 : i] = fmaf(static_cast<float>(static_cast<int32_t>(r[i])), scale, sums[kGroup ? 0 : i]);
+              sums[kGroup ? 0 : i + 1] =
+                  fmaf(static_cast<float>(static_cast<int32_t>(r[i + 1])), scale, sums[kGroup ? 0 : i + 1]);
             }
           }
           if (kDump) {
@@ -495,9 +510,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               if (4 * j + e < my_cols) {
                 float y;
                 if (kGroup) {
-                  y = __fmul_rn(__fsub_rn(sums[4 * j + e], offset_sum), __fmul_rn(rs[e], kScaleDown));
+                  const float2 pair = unpack2(sums2[kGroup ? (4 * j + e) / 2 : 0]);
+                  y = __fmul_rn(__fsub_rn((e & 1) != 0 ? pair.y : pair.x, offset_sum), __fmul_rn(rs[e], kScaleDown));
                 } else {
-                  y = __fmul_rn(__fmul_rn(sums[4 * j + e], rs[e]), wscale);
+                  y = __fmul_rn(__fmul_rn(sums[kGroup ? 0 : 4 * j + e], rs[e]), wscale);
                 }
                 if (has_bias) y = __fadd_rn(y, bias);
                 const int64_t m = m0 + 4 * j + e;

@@ -21,6 +21,10 @@ struct PrepassFusion {
   int64_t mod_span = 1;              // input rows per modulation row
   int64_t mod_row_stride = 0;        // elements between modulation rows
   int round_after = 0;               // round the result to x's dtype before rotation / quantization
+  // static mode: read the schedule entry from device memory; act_scale / gains passed to launch_prepass are
+  // then the bases of the [calls] and [calls, streams] tables
+  const int32_t* call_index = nullptr;
+  int64_t calls = 0;
   // composite rotation: K = mix_order x (power of two); replaces the block rotation, excludes the fusions above
   const float* mix = nullptr;        // [mix_order, mix_order] of +-1
   int mix_order = 0;

@@ -94,6 +94,9 @@ struct PrepassParams {
   const void* mod_shift;
   int64_t mod_span, mod_row_stride;
   int round_after;
+  // static mode with the schedule entry chosen on the device: act_scale / gains are then the table bases
+  const int32_t* call_index;
+  int64_t calls;
   // composite rotation (kMix): K = mix_order x part, part a power of two in [8, 512]
   const float* mix;      // [mix_order, mix_order] entries +-1, row-major
   int mix_order;
@@ -381,8 +384,14 @@ __global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepas
     } else {
       stream = ((row % p.seq_tokens) < p.seq_tokens + p.span) ? 0 : 1;
     }
-    const float scale = __ldg(p.act_scale);
-    const float gain = __ldg(p.gains + (row_ok ? stream : 0));
+    int64_t entry = 0;
+    if (p.call_index != nullptr) {
+      // clamped: a stale or wild index must not read outside the tables
+      const int64_t wanted = __ldg(p.call_index);
+      entry = wanted < 0 ? 0 : (wanted >= p.calls ? p.calls - 1 : wanted);
+    }
+    const float scale = __ldg(p.act_scale + entry);
+    const float gain = __ldg(p.gains + entry * p.streams + (row_ok ? stream : 0));
     multiplier = __fdiv_rn(gain, scale);
     if (row_ok && t == 0) p.row_scales[row] = __fdiv_rn(scale, gain);
   }
@@ -506,6 +515,7 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
   if (mode == SQ_ACT_STATIC) {
     if (act_scale == nullptr || gains == nullptr) return SQ_ERR_NULL;
     if (streams <= 0 || span == 0) return SQ_ERR_SHAPE;
+    if (f.call_index != nullptr && f.calls <= 0) return SQ_ERR_INDEX;
     if (span < 0 && (seq_tokens <= 0 || -span >= seq_tokens || streams != 2)) return SQ_ERR_SHAPE;
   }
   // threads per row: smallest power of two in [32, 512] that leaves at most 4 vectors per thread
@@ -528,6 +538,7 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
   p.norm_kind = f.norm_kind; p.norm_eps = f.norm_eps; p.norm_weight = f.norm_weight;
   p.mod_scale = f.mod_scale; p.mod_shift = f.mod_shift;
   p.mod_span = f.mod_span > 0 ? f.mod_span : 1; p.mod_row_stride = f.mod_row_stride; p.round_after = f.round_after;
+  p.call_index = f.call_index; p.calls = f.calls;
   p.mix = f.mix; p.mix_order = f.mix_order; p.mix_part_log2 = part_log2;
   p.mix_part_norm = static_cast<float>(1.0 / std::sqrt(static_cast<double>(int64_t{1} << part_log2)));
   p.mix_order_root = static_cast<float>(std::sqrt(static_cast<double>(f.mix_order > 0 ? f.mix_order : 1)));

@@ -56,9 +56,12 @@ def stream_span(x, gains, token_counts, activation_scales, *, strict_positive: b
 
 def scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, *, abits, signs=None,
                      rht_block=GROUP, **fused):
+    # `call` is the reference's Python int, or a one-element CUDA int32 tensor read when the kernels run
+    index = call if isinstance(call, torch.Tensor) else None
     return native.linear(x, packed, scales, bias, abits=abits, mode="static", inverse=inverse, signs=signs,
                          rht_block=rht_block, act_scales=activation_scales.contiguous(), gains=gains.contiguous(),
-                         call=int(call), span=span, streams=gains.shape[-1], **fused)
+                         call=0 if index is not None else int(call), call_index=index, span=span,
+                         streams=gains.shape[-1], **fused)
 
 
 def equal_stream_span(x, gains, token_counts, tag: str) -> int:

@@ -111,7 +111,8 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
            span: int = 1, streams: int = 1, out: torch.Tensor | None = None,
            workspace: torch.Tensor | None = None, norm: str | None = None, norm_eps: float = 1e-6, norm_weight=None,
            mod_scale=None, mod_shift=None, round_after_norm: bool = False, activation: str | None = None,
-           gate=None, residual=None, input_activation: str | None = None, mix=None) -> torch.Tensor:
+           gate=None, residual=None, input_activation: str | None = None, mix=None,
+           call_index: torch.Tensor | None = None) -> torch.Tensor:
     """One whole quantized linear (pre-pass + GEMM) through ``sq_linear_fused``.  ``out`` and ``workspace``
     (uint8, at least ``sq_workspace_bytes(rows, K)``) may be passed to reuse buffers across calls.
 
@@ -119,7 +120,11 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
     modulation ``(1 + mod_scale) * y + mod_shift`` in front of the quantizer (one modulation row per equal
     share of the input rows), optionally rounded to x's dtype (``round_after_norm``); ``activation="gelu"``,
     ``gate`` (one row per equal share of the output rows) and ``residual`` behind the GEMM:
-    ``out = residual + gate * act(linear(x))``."""
+    ``out = residual + gate * act(linear(x))``.
+
+    ``call_index`` (a CUDA int32 tensor of one element) makes static mode read its schedule entry from device
+    memory when the kernel runs instead of taking ``call`` on the host: one captured graph then serves every
+    denoise call."""
     _require_cuda(x, "x")
     x = x.contiguous()
     k = x.shape[-1]
@@ -140,7 +145,7 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
     if mix is not None:
         # composite rotation (order x power of two); a rotated site takes no block fusion (runtime.py:75-78)
         if (norm is not None or mod_scale is not None or gate is not None or residual is not None
-                or activation is not None or input_activation is not None):
+                or activation is not None or input_activation is not None or call_index is not None):
             raise ValueError("the composite rotation cannot be combined with fused block work.")
         mix = _mix_matrix(mix, x)
         with torch.cuda.device(x.device):
@@ -170,18 +175,21 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
         gate_span = rows // gate_rows
     if residual is not None:
         residual = residual.contiguous()
+    if call_index is not None and (call_index.dtype != torch.int32 or call_index.numel() != 1
+                                   or call_index.device != x.device):
+        raise ValueError("call_index must be a one-element int32 tensor on the input's device.")
     with torch.cuda.device(x.device):
-        status = lib.sq_linear_fused(
+        status = lib.sq_linear_scheduled(
             x.data_ptr(), _DTYPES[x.dtype], rows, k, n, int(abits),
             _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
             _ptr(inverse), _ptr(signs), int(rht_block), _ptr(act_scales), _ptr(gains), int(calls), int(call),
-            int(span), int(streams), int(x.shape[-2]),
+            _ptr(call_index), int(span), int(streams), int(x.shape[-2]),
             packed.data_ptr(), w_scales.data_ptr(), _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32,
             _ptr(bias), _lib.ACT_FN_GELU if input_activation == "gelu" else _lib.ACT_FN_NONE, norm_kind, float(norm_eps), _ptr(norm_weight), mod_ptr, shift_ptr, int(mod_span),
             int(mod_stride), int(bool(round_after_norm)),
             _lib.ACT_FN_NONE, gate_ptr, int(gate_span), int(gate_stride),
             _ptr(residual), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
-    _lib.check(status, "sq_linear_fused")
+    _lib.check(status, "sq_linear_scheduled")
     if activation == "gelu":  # an output activation is not fused into the GEMM (it measured slower there)
         if gate is not None or residual is not None:
             raise ValueError("an output activation cannot be combined with a fused gate or residual.")

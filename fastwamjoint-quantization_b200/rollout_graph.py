@@ -6,6 +6,12 @@ per-call scale and gains of every quantized linear, so it is part of what a capt
 are copied into the captured tensors before each replay and outputs are cloned before they are returned;
 a changed input layout, schedule length, guidance scale or re-entrant use is refused instead of replaying
 stale data; the first replay of every graph is compared with the eager result.
+
+``single_graph=True`` (needs the model's ``DenoiseCallState``): the state is switched to ``on_device``, so the
+quantized linears read the call index from device memory; ONE graph is captured and replayed for every call
+index, and its first replay at each index is compared with the eager result of that index.  ``clone_outputs=
+False`` returns the captured output tensors themselves (valid until the next replay) and inputs that already
+are the captured tensors (``static_inputs()``) are not copied.
 """
 from __future__ import annotations
 
@@ -50,7 +56,8 @@ def _clone(value):
 
 def _copy(target, source) -> None:
     if isinstance(target, torch.Tensor):
-        target.copy_(source)
+        if target.data_ptr() != source.data_ptr():  # the caller may have written the captured tensor in place
+            target.copy_(source)
     elif isinstance(target, dict):
         for key in target:
             _copy(target[key], source[key])
@@ -60,9 +67,16 @@ def _copy(target, source) -> None:
 
 
 class LiveJointDiTGraph:
-    def __init__(self, model, *, num_calls: int = 10, warmup: int = 2, allow_numerical_mismatch: bool = False):
+    def __init__(self, model, *, num_calls: int = 10, warmup: int = 2, allow_numerical_mismatch: bool = False,
+                 single_graph: bool = False, state=None, clone_outputs: bool = True):
         if num_calls <= 0 or warmup < 1:
             raise ValueError("Graph calls and warmup must be positive.")
+        if single_graph:
+            state = state if state is not None else getattr(getattr(model, "_wam_call_tracker", None), "state", None)
+            if state is None:
+                raise ValueError("single_graph needs the model's DenoiseCallState (state=...).")
+        self.single_graph, self.state, self.clone_outputs = single_graph, state, clone_outputs
+        self._validated: set[int] = set()
         self.model = model
         self.num_calls, self.warmup = num_calls, warmup
         self.allow_numerical_mismatch = allow_numerical_mismatch
@@ -106,6 +120,9 @@ class LiveJointDiTGraph:
             finally:
                 self._active = False
 
+        if self.single_graph:
+            self._state_was_on_device = self.state.on_device
+            self.state.on_device = True
         self.model._joint_denoise_core = self._call
         self.model.infer_action = infer
         self.model._rollout_graph = self
@@ -124,10 +141,19 @@ class LiveJointDiTGraph:
             else:
                 setattr(self.model, name, previous)
         delattr(self.model, "_rollout_graph")
+        if self.single_graph:
+            self.state.on_device = self._state_was_on_device
+        self._validated.clear()
         self.entries.clear()
         self._installed = False
 
     # ------------------------------------------------------------------ the replaced core
+    def static_inputs(self, index: int = 0):
+        """``(args, kwargs)`` of captured input tensors of graph ``index`` (the only graph in single-graph mode):
+        a caller that writes its inputs there and passes them in skips the copy-in."""
+        _, static_args, static_kwargs, _, _ = self.entries[0 if self.single_graph else index]
+        return static_args, static_kwargs
+
     def _capture(self, index: int, values, signature):
         static_args, static_kwargs = _clone(values)
         side = torch.cuda.Stream()
@@ -143,7 +169,8 @@ class LiveJointDiTGraph:
         graph.replay()
         torch.cuda.synchronize()
         self._validate_outputs(outputs, expected, index)
-        self.entries[index] = (signature, static_args, static_kwargs, graph, outputs)
+        self._validated.add(index)
+        self.entries[0 if self.single_graph else index] = (signature, static_args, static_kwargs, graph, outputs)
         log.warning("[live DiT Graph] captured step %d/%d (validation mode=%s)", index + 1, self.num_calls,
                     "warn" if self.allow_numerical_mismatch else "strict")
 
@@ -158,20 +185,28 @@ class LiveJointDiTGraph:
             raise RuntimeError("WAM call state does not match live Graph index.")
         values = (args, kwargs)
         signature = _signature(values)
-        if index not in self.entries:
+        key = 0 if self.single_graph else index
+        if self.single_graph and self.state.require() != index:
+            raise RuntimeError("WAM call state does not match live Graph index.")
+        if key not in self.entries:
             self._capture(index, values, signature)
-        captured_signature, static_args, static_kwargs, graph, outputs = self.entries[index]
+        captured_signature, static_args, static_kwargs, graph, outputs = self.entries[key]
         if signature != captured_signature:
             raise ValueError("Live DiT Graph input layout/constants changed; refusing stale replay.")
         _copy((static_args, static_kwargs), values)
         graph.replay()
+        if self.single_graph and index not in self._validated:
+            # the one graph at a call index it has not run at yet: compare with the eager result of this index
+            expected = self.original_core(*static_args, **static_kwargs)
+            self._validate_outputs(outputs, expected, index)
+            self._validated.add(index)
         if self.allow_numerical_mismatch:  # opt-in runs still reject non-finite outputs on every replay
             for output in outputs:
                 if not torch.isfinite(output).all():
                     raise RuntimeError("Nonfinite live Graph output during replay.")
         self.replays += 1
         self.calls += 1
-        return _clone(outputs)
+        return _clone(outputs) if self.clone_outputs else outputs
 
     def _validate_outputs(self, outputs, expected, index):
         """First replay against the eager result: same count / layout, finite, close to 1e-3

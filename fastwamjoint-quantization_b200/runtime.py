@@ -158,10 +158,19 @@ class WAMQuantLinear(nn.Module):
             raise RuntimeError(f"WAM {what} stream names differ from {self.site.module_name}: {layout.names}.")
         return layout
 
+    def _call(self, x: torch.Tensor):
+        """The active call for a native launch: the Python index, or - when the state is ``on_device`` - the
+        state's device tensor, which the kernels read when they run (one graph for all calls)."""
+        call = self.state.require()
+        if getattr(self.state, "on_device", False):
+            return self.state.device_index(x.device)
+        return call
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         call = self.state.require()
         layout = self._layout(x, "checkpoint")
         if self.backend != "reference":
+            call = self._call(x)
             args = (x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges,
                     self.gamma_gains, layout.token_counts, call)
             if self.input_rotation_signs is not None:
@@ -195,7 +204,7 @@ class WAMQuantLinear(nn.Module):
         layout = self._layout(x, "fused AdaLN")
         return self._native_ops.symmetric_scheduled_stream_adaln_linear(
             x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
-            layout.token_counts, self.state.require(), scale, shift, epsilon)
+            layout.token_counts, self._call(x), scale, shift, epsilon)
 
     def forward_gate_residual(self, x, residual, gate):
         if not self.supports_fused_gate_residual:
@@ -203,7 +212,7 @@ class WAMQuantLinear(nn.Module):
         layout = self._layout(x, "fused residual")
         return self._native_ops.symmetric_scheduled_stream_gate_residual_linear(
             x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
-            layout.token_counts, self.state.require(), residual, gate)
+            layout.token_counts, self._call(x), residual, gate)
 
 
 def set_wam_block_fusions(model: nn.Module, enabled: bool) -> int:

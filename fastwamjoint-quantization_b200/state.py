@@ -1,9 +1,15 @@
 """Which denoise call is running.  Same names and behaviour as the reference's ``state.py:10-71``:
-modules read ``state.require()`` to pick their per-call activation scale and stream gains."""
+modules read ``state.require()`` to pick their per-call activation scale and stream gains.
+
+Addition: ``on_device``.  When it is set, native modules do not bake the Python index into their launches but
+pass ``device_index(device)``, a one-element int32 tensor that ``set()`` keeps equal to the index; the kernels
+read the schedule entry from it when they run, so one captured CUDA graph serves every call."""
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, Callable
+
+import torch
 
 
 @dataclass
@@ -12,6 +18,8 @@ class DenoiseCallState:
 
     num_calls: int
     index: int | None = None
+    on_device: bool = False
+    _mirrors: dict = field(default_factory=dict, repr=False, compare=False)
 
     def __post_init__(self) -> None:
         if self.num_calls <= 0:
@@ -22,6 +30,18 @@ class DenoiseCallState:
         if value < 0 or value >= self.num_calls:
             raise IndexError(f"Denoise call {value} is outside [0, {self.num_calls}).")
         self.index = value
+        for mirror in self._mirrors.values():
+            mirror.fill_(value)  # on the current stream, ordered before the next launch or graph replay
+
+    def device_index(self, device) -> torch.Tensor:
+        """One-element int32 tensor on ``device`` holding the active index (created on first use; creating it
+        allocates, so ask for it once before a stream capture)."""
+        device = torch.device(device)
+        mirror = self._mirrors.get(device)
+        if mirror is None:
+            mirror = torch.full((1,), self.require(), device=device, dtype=torch.int32)
+            self._mirrors[device] = mirror
+        return mirror
 
     def require(self) -> int:
         if self.index is None:

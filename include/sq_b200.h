@@ -187,6 +187,22 @@ int sq_linear_fused(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t
                     const void* residual,
                     void* out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* sq_linear_fused with the schedule entry chosen on the device: when `call_index` (device int32) is not null,
+ * static mode reads act_scales[*call_index] and gains[*call_index, :] when the kernel runs (clamped to
+ * [0, calls)); `call` is then ignored.  One captured CUDA graph serves every denoise call: the host changes the
+ * integer between replays.  The reference bakes the entry into each capture (pointer arithmetic on the host,
+ * w4a8.cu:1362-1363) and therefore keeps one graph per call (rollout_graph.py:111-155). */
+int sq_linear_scheduled(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
+                        const float* inv_d, const float* signs, int rht_block,
+                        const float* act_scales, const float* gains, int64_t calls, int64_t call,
+                        const int32_t* call_index, int64_t span, int64_t streams, int64_t seq_tokens,
+                        const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
+                        int input_activation, int norm_kind, float norm_eps, const void* norm_weight,
+                        const void* mod_scale, const void* mod_shift, int64_t mod_span, int64_t mod_row_stride,
+                        int round_after_norm, int activation, const void* gate, int64_t gate_span,
+                        int64_t gate_row_stride, const void* residual,
+                        void* out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* sq_linear for callers that cannot allocate device memory.  It has no counterpart in the reference, whose
  * operators always allocate their scratch per call (torch::empty, w4a8.cu:1358-1360).
  *

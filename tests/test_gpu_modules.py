@@ -256,6 +256,78 @@ def test_live_graph_capture_replay_and_refusals(m):
     assert not hasattr(model, "_rollout_graph")
 
 
+def test_single_graph_for_all_calls(m):
+    """One captured graph replayed at every call index: the linears read the index from device memory, so the
+    outputs equal the per-call eager results bit for bit, one capture exists, and every index was validated once."""
+    R, G = m["runtime"], m["rollout_graph"]
+    torch.manual_seed(1)
+    source = torch.nn.Linear(256, 8, bias=False, device="cuda", dtype=torch.bfloat16)
+    state = m["state"].DenoiseCallState(2)
+    layer = R.WAMQuantLinear(source, _entry(m, False), state=state, stream_config=m["streams"].FastWAMStreamConfig(),
+                             weight_bits=4, activation_bits=4, backend="cutlass_w4a4")
+    model = Tiny(layer, state, 2)
+    values = (0.3, -0.7, 1.1)
+    eager = [model.infer_action(torch.full((1, 32, 256), v, device="cuda", dtype=torch.bfloat16)) for v in values]
+    assert not torch.equal(eager[0][0], eager[0][1])  # the two calls of the schedule really differ
+    glue = G.LiveJointDiTGraph(model, num_calls=2, warmup=1, single_graph=True, state=state).install()
+    with torch.no_grad():
+        for v, want in zip(values, eager):
+            got = model.infer_action(torch.full((1, 32, 256), v, device="cuda", dtype=torch.bfloat16))
+            assert torch.equal(got, want)
+        assert len(glue.entries) == 1 and glue.replays == 6
+        assert sorted(r["step"] for r in glue.validation_records) == [0, 1] and all(r["passed"] for r in glue.validation_records)
+        # inputs written in place, outputs not cloned
+        glue.clone_outputs = False
+        (static_tokens,), _ = glue.static_inputs()
+        static_tokens.fill_(values[1])
+        got = model.infer_action(static_tokens)
+        # both calls returned the one captured output tensor, which now holds the last call's result
+        assert torch.equal(got[1], eager[1][1]) and torch.equal(got[0], got[1])
+        with pytest.raises(ValueError, match="layout"):
+            model.infer_action(torch.zeros(1, 64, 256, device="cuda", dtype=torch.bfloat16))
+    glue.remove()
+    assert state.on_device is False and not hasattr(model, "_rollout_graph")
+    with pytest.raises(ValueError, match="DenoiseCallState"):
+        G.LiveJointDiTGraph(model, num_calls=2, single_graph=True)
+
+
+@pytest.mark.parametrize("abits", [8, 4])
+def test_device_call_index_equals_host_call(m, oracle, abits):
+    """The schedule entry read from a device int32 equals the host-indexed call, also through one captured graph
+    replayed with a changed index; an index outside the table is clamped, not followed."""
+    ops = m["ops8"] if abits == 8 else m["ops4"]
+    gen = torch.Generator().manual_seed(5)
+    rows, k, n, calls = 64, 512, 256, 4
+    x = (torch.randn(1, rows, k, generator=gen) * 1.5).bfloat16().cuda()
+    packed = m["ops8"].pack_signed_int4(torch.randint(-7, 8, (n, k), generator=gen, dtype=torch.int8)).cuda()
+    scales = torch.full((n,), 0.002).cuda()
+    inverse = torch.ones(k).cuda()
+    act = torch.linspace(0.02, 0.08, calls).cuda() * (16 if abits == 4 else 1)
+    gains = (torch.rand(calls, 2, generator=gen) + 0.5).cuda()
+    run = lambda call: ops.symmetric_scheduled_stream_linear(x, packed, scales, None, inverse, act, gains, (32, 32), call)
+    host = [run(c) for c in range(calls)]
+    assert not torch.equal(host[0], host[1])
+    index = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for c in range(calls):
+        index.fill_(c)
+        assert torch.equal(run(index), host[c])
+    graph = torch.cuda.CUDAGraph()
+    index.fill_(0)
+    run(index)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph):
+        captured = run(index)
+    for c in (3, 1, 0, 2):
+        index.fill_(c)
+        graph.replay()
+        assert torch.equal(captured, host[c])
+    for wild, clamped in ((-5, 0), (99, calls - 1)):
+        index.fill_(wild)
+        assert torch.equal(run(index), host[clamped])
+    with pytest.raises(ValueError, match="int32"):
+        run(torch.zeros(1, dtype=torch.int64, device="cuda"))
+
+
 @pytest.mark.parametrize("abits,rotate", [(8, False), (4, True)])
 def test_small_dit_stack_native_vs_reference_and_graph(m, abits, rotate):
     """Two blocks of the synthetic DiT at reduced width: native kernels against the fake-quant backend on the
