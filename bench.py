@@ -36,12 +36,13 @@ WORKLOADS = {
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch from the committed ncu capture
 # (profiles/sq_gemm_tc_kernel_c2_w4a4_rht.md); other workloads have no capture
-NCU_TRAFFIC_BYTES = {"c2": 11.20e6}
+NCU_TRAFFIC_BYTES = {("c2", "packed"): 11.26e6}
 
 
-def algorithmic_bytes(m, k, n, rotate):
-    """bf16 x + int4 w + fp16 group scales + bias + bf16 out (+ fp32 signs)."""
-    return 2 * m * k + n * k // 2 + 2 * n * (k // 128) + 2 * n + 2 * m * n + (4 * k if rotate else 0)
+def algorithmic_bytes(m, k, n, rotate, weights="packed"):
+    """bf16 x + weights (int4 packed, or int8 prepacked) + fp16 group scales + bias + bf16 out (+ fp32 signs)."""
+    w_bytes = n * k if weights == "prepacked" else n * k // 2
+    return 2 * m * k + w_bytes + 2 * n * (k // 128) + 2 * n + 2 * m * n + (4 * k if rotate else 0)
 
 
 def load_oracle():
@@ -265,6 +266,8 @@ def run_dit(args):
     from fastwamjoint_quantization_b200 import dit, native
     cfg = dit.DiTConfig(activation_bits=abits, rotate=rotate)
     model = dit.SyntheticDiT(cfg, device=device, backend="native")
+    if args.weights == "prepacked":
+        model.prepack()
     x = torch.randn(1, cfg.tokens, cfg.hidden, generator=torch.Generator(device=device).manual_seed(0),
                     device=device).bfloat16()
     x_host = x.cpu().pin_memory()
@@ -347,7 +350,8 @@ def run_dit(args):
             "config": {"workload": args.workload, "blocks": 30, "hidden": 3072, "heads": 24, "ffn": 12288,
                        "tokens": cfg.tokens, "abits": abits, "rht": rotate, "replicas": world,
                        "launch": "one CUDA graph per step",
-                       "l2": "1.7 GB of packed weights streamed per step (> 126 MB L2)"},
+                       "weights": args.weights,
+                       "l2": "%s GB of weights streamed per step (> 126 MB L2)" % ("3.4" if args.weights == "prepacked" else "1.7")},
             "gpu_launches": 240 * args.steps,
             "linear_tops": linear_ops / (ms * 1e-3) / 1e12,
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": x_host.numel() * 2,
@@ -366,6 +370,9 @@ def main():
     parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(DIT_WORKLOADS) + ["nsplit_ffn_up"])
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--weights", default="prepacked", choices=["prepacked", "packed"],
+                        help="prepacked: the int8 operand form made once at load time from the packed int4 "
+                             "checkpoint format (sq_prepack_weights); packed: the checkpoint format itself")
     args = parser.parse_args()
     if args.workload == "nsplit_ffn_up":
         if args.steps == 200:
@@ -407,12 +414,13 @@ def main():
     signs = None if case["signs"] is None else case["signs"].to(device)
 
     # rotating input sets so every step reads x and W from HBM, not from L2
-    set_bytes = algorithmic_bytes(m, k, n, rotate)
+    set_bytes = algorithmic_bytes(m, k, n, rotate, args.weights)
     nsets = max(2, -(-2 * L2_BYTES // set_bytes))
     xs, packs, wss = [], [], []
     for i in range(nsets):
         xs.append((case["x"].float() * (1.0 + 0.001 * i)).to(torch.bfloat16).to(device))
-        packs.append(packed_host.to(device).clone())
+        packs.append(native.prepack_weights(packed_host.to(device)) if args.weights == "prepacked"
+                     else packed_host.to(device).clone())
         wss.append(case["weight_scales"].to(device).clone())
     bias = case["bias"].to(device)
 
@@ -570,13 +578,13 @@ def main():
             int8_source = "2 x measured bf16 peak (torch._int_mm failed: %s)" % type(exc).__name__
         gemm_tops = ops_per_step / (gemm_ms * 1e-3) / 1e12
         t_compute = ops_per_step / (int8_peak * 1e12)
-        t_hbm = algorithmic_bytes(m, k, n, rotate) / (hbm_peak * 1e9)
+        t_hbm = algorithmic_bytes(m, k, n, rotate, args.weights) / (hbm_peak * 1e9)
         if t_compute >= t_hbm:
             roofline = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s",
-                        "frac": gemm_tops / int8_peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                        "frac": gemm_tops / int8_peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.weights)),
                         "peak_source": int8_source}
         else:
-            gbs = algorithmic_bytes(m, k, n, rotate) / (gemm_ms * 1e-3) / 1e9
+            gbs = algorithmic_bytes(m, k, n, rotate, args.weights) / (gemm_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
                         "traffic": None, "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"}
         roofline["kernel"] = "sq_gemm_tc_kernel"
@@ -590,6 +598,8 @@ def main():
             "dtype": "int8 x int4 -> int32", "data": "synthetic",
             "config": {"workload": args.workload, "M_per_gpu": m, "K": k, "N": n, "abits": abits, "rht": rotate,
                        "weight_scales": "fp16 group-128", "activation_scales": "per-token",
+                       "weights": ("int8 operand form, prepacked once at load from the packed int4 format"
+                                   if args.weights == "prepacked" else "packed int4 (checkpoint format)"),
                        "sharding": "tokens (M) across ranks, weights replicated, no collective",
                        "l2": "rotating %d input sets (%.0f MB > 126 MB L2)" % (nsets, nsets * set_bytes / 1e6),
                        "launch": "the K steps are replayed as one CUDA graph"},

@@ -19,6 +19,7 @@ NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024 + 65536
 BF16, FP16 = 0, 1
 ACT_STATIC, ACT_TOKEN = 0, 1
 CODES_NATURAL, CODES_EVEN_ODD = 0, 1
+WEIGHTS_PREPACKED = 4  # OR-ed onto the weight-scale mode: weights are int8 [N, K] from sq_prepack_weights
 CODES_INT4_RANGE = 2  # OR-ed onto the layout for sq_gemm: every code lies in [-8, 7]
 WSCALE_CHANNEL_F32, WSCALE_GROUP_F16 = 0, 1
 NORM_NONE, NORM_LAYER, NORM_RMS = 0, 1, 2
@@ -33,6 +34,7 @@ _SIGNATURES = {
                               c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "sq_gemm_timeline": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_void_p, c_void_p]),
+    "sq_prepack_weights": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "sq_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "sq_linear": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -42,7 +42,32 @@ int validate_gemm(const GemmArgs& a) {
   if (a.wscale_mode == SQ_WSCALE_GROUP_F16 && a.K % 128 != 0) return SQ_ERR_SHAPE;
   if (a.M > (int64_t{1} << 30) || a.N > (int64_t{1} << 30) || a.K > 131072) return SQ_ERR_SHAPE;
   if (!aligned16(a.codes) || !aligned16(a.w_packed) || !aligned16(a.out)) return SQ_ERR_SHAPE;
+  // unpacked weights are stored in the even-odd k order and carry no path for the accumulator dump
+  if (a.weights_prepacked && (a.codes_layout != SQ_CODES_EVEN_ODD || a.acc_dump != nullptr)) return SQ_ERR_ENUM;
   return SQ_OK;
+}
+
+// ------------------------------------------------------------------ weight prepack
+// One thread per packed 32-bit word (8 consecutive k of one channel): the unpack the GEMM's converter warps do
+// per tile, done once.  Output bytes: 16 w of k0 k2 k4 k6, then of k1 k3 k5 k7.
+__global__ void sq_prepack_kernel(const uint32_t* __restrict__ packed, uint2* __restrict__ tiled, int64_t words) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= words) return;
+  const uint32_t w = __ldg(packed + i);
+  tiled[i] = make_uint2((w << 4) & 0xF0F0F0F0u, w & 0xF0F0F0F0u);
+}
+
+int launch_prepack_weights(const uint8_t* w_packed, int64_t N, int64_t K, int8_t* w_tiled, cudaStream_t stream) {
+  if (w_packed == nullptr || w_tiled == nullptr) return SQ_ERR_NULL;
+  if (N <= 0 || K <= 0 || K % 32 != 0 || N > (int64_t{1} << 30) || K > 131072) return SQ_ERR_SHAPE;
+  if (!aligned16(w_packed) || !aligned16(w_tiled)) return SQ_ERR_SHAPE;
+  const int64_t words = N * (K / 8);
+  const int threads = 256;
+  const int64_t blocks = (words + threads - 1) / threads;
+  sq_prepack_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+      reinterpret_cast<const uint32_t*>(w_packed), reinterpret_cast<uint2*>(w_tiled), words);
+  const cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
 }
 
 // ------------------------------------------------------------------ cross-check GEMM (CUDA cores)
@@ -102,6 +127,7 @@ __global__ void sq_gemm_check_kernel(const int8_t* __restrict__ codes, int even_
 int launch_gemm_check(const GemmArgs& a, cudaStream_t stream) {
   int v = validate_gemm(a);
   if (v != SQ_OK) return v;
+  if (a.weights_prepacked) return SQ_ERR_ENUM;  // the cross-check reads the packed int4 form only
   if (a.M == 0) return SQ_OK;
   if (a.M > 65535) return SQ_ERR_SHAPE;
   const dim3 block(128);
@@ -171,7 +197,8 @@ static sq::GemmArgs make_args(const void* codes, int codes_layout, const void* w
   a.codes_int4_range = (codes_layout & SQ_CODES_INT4_RANGE) != 0;
   a.w_packed = static_cast<const uint8_t*>(w_packed);
   a.w_scales = w_scales;
-  a.wscale_mode = wscale_mode;
+  a.wscale_mode = wscale_mode & ~SQ_WEIGHTS_PREPACKED;
+  a.weights_prepacked = (wscale_mode & SQ_WEIGHTS_PREPACKED) != 0;
   a.row_scales = row_scales;
   a.bias = bias;
   a.out = out;
@@ -204,6 +231,11 @@ int sq_gemm_timeline(const void* codes, const void* w_packed, const void* w_scal
   return sq::launch_gemm_timeline(make_args(codes, SQ_CODES_EVEN_ODD, w_packed, w_scales, SQ_WSCALE_GROUP_F16, row_scales,
                                             bias, out, SQ_BF16, M, N, K, nullptr),
                                   timeline, static_cast<cudaStream_t>(stream));
+}
+
+int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled, void* stream) {
+  return sq::launch_prepack_weights(static_cast<const uint8_t*>(w_packed), N, K, static_cast<int8_t*>(w_tiled),
+                                    static_cast<cudaStream_t>(stream));
 }
 
 size_t sq_workspace_bytes(int64_t M, int64_t K) {

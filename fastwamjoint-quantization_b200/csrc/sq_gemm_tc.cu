@@ -150,7 +150,9 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
 // kGroup one accumulator per 128-K weight group (fp16 scales [N, K/128]); otherwise one per tile (fp32 [N])
 // kEvenOdd codes are stored even-k-first inside each run of 8 (no byte interleave needed when unpacking)
 // kDump  also write the exact integer accumulators
-template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
+// kPre   the weights arrive already unpacked (int8 = 16 w, even-odd k order, from sq_prepack_weights): TMA puts
+//        them straight into the operand tile and the unpack warps have nothing to do
+template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TcParams p) {
@@ -192,7 +194,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_wfull + 8 * s, kNumConverterWarps);
+      mbar_init(bar_wfull + 8 * s, kPre ? 1 : kNumConverterWarps);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < static_cast<int>(kAccBufs); ++b) {
@@ -251,10 +253,17 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             // The codes land on the barrier the MMA warps wait on (together with the unpack warps'
             // arrivals), the packed weights on the barrier the unpack warps wait on.  The expect_tx on
             // bar_wfull is issued before the packed load, so no unpack warp can arrive for this phase first.
-            mbar_expect_tx(bar_wfull + 8 * s, static_cast<uint32_t>(p.tok_tile) * kBlockK);
-            mbar_arrive_expect_tx(bar_full + 8 * s, kPackedBytes);
-            tma_load_2d(x_ring + s * kXBytes, &tmap_codes, kb * kBlockK, tok0, bar_wfull + 8 * s);
-            tma_load_2d(p_ring + s * kPackedBytes, &tmap_packed, kb * (kBlockK / 2), ch0, bar_full + 8 * s);
+            if (kPre) {
+              // both operand tiles land on the barrier the MMA warps wait on
+              mbar_arrive_expect_tx(bar_wfull + 8 * s, static_cast<uint32_t>(p.tok_tile) * kBlockK + kWBytes);
+              tma_load_2d(x_ring + s * kXBytes, &tmap_codes, kb * kBlockK, tok0, bar_wfull + 8 * s);
+              tma_load_2d(w_ring + s * kWBytes, &tmap_packed, kb * kBlockK, ch0, bar_wfull + 8 * s);
+            } else {
+              mbar_expect_tx(bar_wfull + 8 * s, static_cast<uint32_t>(p.tok_tile) * kBlockK);
+              mbar_arrive_expect_tx(bar_full + 8 * s, kPackedBytes);
+              tma_load_2d(x_ring + s * kXBytes, &tmap_codes, kb * kBlockK, tok0, bar_wfull + 8 * s);
+              tma_load_2d(p_ring + s * kPackedBytes, &tmap_packed, kb * (kBlockK / 2), ch0, bar_full + 8 * s);
+            }
           }
           __syncwarp();
         }
@@ -327,7 +336,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     const int ctid = threadIdx.x - 128;  // 0..127
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = blockIdx.x; !kPre && tile < num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
         const uint32_t s = it % S, phase = (it / S) & 1u;
         if (!mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs)) {
@@ -600,9 +609,9 @@ int pick_tok_tile(int64_t M, int ch_tiles, int sms) {
   return best;
 }
 
-template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false>
+template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false>
 int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long long* timeline = nullptr) {
-  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace>;
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre>;
   constexpr uint32_t smem = smem_bytes_for(TOK);
   static bool configured[64] = {false};
   int dev = 0;
@@ -616,9 +625,14 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   if (!make_map(&tmap_codes, a.codes, static_cast<uint64_t>(a.M), static_cast<uint64_t>(a.K),
                 static_cast<uint32_t>(tok_tile), kBlockK, CU_TENSOR_MAP_SWIZZLE_128B))
     return SQ_ERR_DRIVER;
-  if (!make_map(&tmap_packed, a.w_packed, static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 2), kBlockCh,
-                kBlockK / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
+  if (kPre) {
+    if (!make_map(&tmap_packed, a.w_packed, static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K), kBlockCh, kBlockK,
+                  CU_TENSOR_MAP_SWIZZLE_128B))
+      return SQ_ERR_DRIVER;
+  } else if (!make_map(&tmap_packed, a.w_packed, static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 2), kBlockCh,
+                       kBlockK / 2, CU_TENSOR_MAP_SWIZZLE_NONE)) {
     return SQ_ERR_DRIVER;
+  }
   TcParams p;
   p.w_scales = a.w_scales; p.row_scales = a.row_scales; p.bias = a.bias; p.out = a.out;
   p.acc_dump = a.acc_dump; p.timeline = timeline; p.status = device_status_word();
@@ -655,6 +669,10 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
 #define SQ_LAUNCH(EO, DUMP)                                                                          \
   (bf16 ? launch_variant<TOK, kGroup, EO, DUMP, __nv_bfloat16>(a, tok_tile, stream)          \
         : launch_variant<TOK, kGroup, EO, DUMP, __half>(a, tok_tile, stream))
+  if (a.weights_prepacked) {  // validated: even-odd codes, no accumulator dump
+    return bf16 ? launch_variant<TOK, kGroup, true, false, __nv_bfloat16, false, true>(a, tok_tile, stream)
+                : launch_variant<TOK, kGroup, true, false, __half, false, true>(a, tok_tile, stream);
+  }
   if (eo) return dump ? SQ_LAUNCH(true, true) : SQ_LAUNCH(true, false);
   return dump ? SQ_LAUNCH(false, true) : SQ_LAUNCH(false, false);
 #undef SQ_LAUNCH

@@ -47,6 +47,7 @@ struct GemmArgs {
   int out_dtype;
   int64_t M, N, K;
   int32_t* acc_dump;
+  bool weights_prepacked = false;  // SQ_WEIGHTS_PREPACKED: w_packed is int8 [N, K] from sq_prepack_weights
   bool codes_int4_range = false;  // SQ_CODES_INT4_RANGE was set: every code lies in [-8, 7]
   // fused epilogue: out = residual + gate * act(acc * scales + bias)
   int activation = SQ_ACT_FN_NONE;
@@ -57,6 +58,7 @@ struct GemmArgs {
 };
 
 int validate_gemm(const GemmArgs& a);
+int launch_prepack_weights(const uint8_t* w_packed, int64_t N, int64_t K, int8_t* w_tiled, cudaStream_t stream);
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
 int launch_gemm_check(const GemmArgs& a, cudaStream_t stream);
 // Group-scale bf16 GEMM with M > 128 only: same result, plus clock stamps of CTA 0's pipeline roles.

@@ -44,6 +44,17 @@ class TokenQuantLinear(nn.Module):
         self.in_features, self.out_features = k, n
         self._dequantized: torch.Tensor | None = None
         self.workspace: torch.Tensor | None = None  # shared scratch set by the owning stack
+        # optional kernel-native copy of the weight (``prepack()``), used from PREPACK_MIN_ROWS input rows on
+        self.weight_tiled: torch.Tensor | None = None
+
+    PREPACK_MIN_ROWS = 512  # below this the GEMM is bound by weight bytes, which the unpacked form doubles
+
+    def prepack(self) -> "TokenQuantLinear":
+        """Keep a second copy of the weight in the GEMM's operand form (int8 [N, K], ``sq_prepack_weights``):
+        the GEMM then skips its unpack stage.  The packed buffer stays the checkpoint format."""
+        if self.weight.is_cuda and self.weight_tiled is None:
+            self.weight_tiled = native.prepack_weights(self.weight)
+        return self
 
     def _reference_weight(self, dtype):
         if self._dequantized is None or self._dequantized.dtype != dtype:
@@ -63,7 +74,9 @@ class TokenQuantLinear(nn.Module):
         if self.backend == "native":
             # the residual add stays a separate elementwise kernel: in the GEMM epilogue it runs on the drain
             # warps, which set the kernel's pace, and measured 20 % slower than GEMM + add
-            y = native.linear(x, self.weight, self.weight_scales, self.bias, abits=self.activation_bits,
+            rows = x.numel() // x.shape[-1]
+            weight = self.weight_tiled if self.weight_tiled is not None and rows >= self.PREPACK_MIN_ROWS else self.weight
+            y = native.linear(x, weight, self.weight_scales, self.bias, abits=self.activation_bits,
                               mode="token", signs=self.input_rotation_signs, workspace=self.workspace,
                               norm=None if rms_eps is None else "rms", norm_eps=rms_eps or 0.0,
                               round_after_norm=rms_eps is not None, input_activation=input_activation)
@@ -157,6 +170,13 @@ class SyntheticDiT(nn.Module):
             for module in self.modules():
                 if isinstance(module, TokenQuantLinear):
                     module.workspace = self.workspace
+
+    def prepack(self) -> "SyntheticDiT":
+        """Give every linear a kernel-native copy of its weight (see ``TokenQuantLinear.prepack``)."""
+        for module in self.modules():
+            if isinstance(module, TokenQuantLinear):
+                module.prepack()
+        return self
 
     def set_backend(self, backend: str) -> None:
         for module in self.modules():

@@ -63,6 +63,25 @@ def prepass(x: torch.Tensor, *, abits: int, mode: str, inverse=None, signs=None,
     return codes, row_scales
 
 
+def prepack_weights(packed: torch.Tensor) -> torch.Tensor:
+    """uint8 [N, K/2] packed int4 weights -> int8 [N, K] in the GEMM's own operand form (``sq_prepack_weights``).
+    Pass the result wherever ``packed`` goes: ``gemm`` and ``linear`` tell the two forms apart by dtype."""
+    _require_cuda(packed, "packed")
+    if packed.dtype != torch.uint8 or packed.ndim != 2 or not packed.is_contiguous():
+        raise ValueError("packed must be a contiguous uint8 [N, K/2] tensor.")
+    n, half = packed.shape
+    tiled = torch.empty((n, 2 * half), device=packed.device, dtype=torch.int8)
+    with torch.cuda.device(packed.device):
+        status = _lib.load_library().sq_prepack_weights(packed.data_ptr(), n, 2 * half, tiled.data_ptr(), _stream())
+    _lib.check(status, "sq_prepack_weights")
+    return tiled
+
+
+def _wscale_mode(packed: torch.Tensor, w_scales: torch.Tensor) -> int:
+    mode = _lib.WSCALE_GROUP_F16 if w_scales.dtype == torch.float16 else _lib.WSCALE_CHANNEL_F32
+    return mode | (_lib.WEIGHTS_PREPACKED if packed.dtype == torch.int8 else 0)
+
+
 def _mix_matrix(mix: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     if mix.ndim != 2 or mix.shape[0] != mix.shape[1] or mix.dtype != torch.float32 or mix.device != x.device:
         raise ValueError("mix must be a square fp32 matrix on the input's device.")
@@ -89,7 +108,7 @@ def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_
     fn = lib.sq_gemm_check if check_kernel else lib.sq_gemm
     with torch.cuda.device(codes.device):
         status = fn(codes.data_ptr(), int(codes_layout) | (_lib.CODES_INT4_RANGE if int4_range else 0), packed.data_ptr(), w_scales.data_ptr(),
-                    _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32, row_scales.data_ptr(), _ptr(bias),
+                    _wscale_mode(packed, w_scales), row_scales.data_ptr(), _ptr(bias),
                     out.data_ptr(), _DTYPES[out_dtype], m, n, k, _ptr(acc), _stream())
     _lib.check(status, "sq_gemm_check" if check_kernel else "sq_gemm")
     return (out, acc) if want_accumulators else out
@@ -154,7 +173,7 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
                 _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
                 _ptr(inverse), _ptr(signs), mix.data_ptr(), int(mix.shape[0]), _ptr(act_scales), _ptr(gains),
                 int(calls), int(call), int(span), int(streams), int(x.shape[-2]),
-                packed.data_ptr(), w_scales.data_ptr(), _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32,
+                packed.data_ptr(), w_scales.data_ptr(), _wscale_mode(packed, w_scales),
                 _ptr(bias), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
         _lib.check(status, "sq_linear_composite")
         return out
@@ -184,7 +203,7 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
             _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
             _ptr(inverse), _ptr(signs), int(rht_block), _ptr(act_scales), _ptr(gains), int(calls), int(call),
             _ptr(call_index), int(span), int(streams), int(x.shape[-2]),
-            packed.data_ptr(), w_scales.data_ptr(), _lib.WSCALE_GROUP_F16 if group else _lib.WSCALE_CHANNEL_F32,
+            packed.data_ptr(), w_scales.data_ptr(), _wscale_mode(packed, w_scales),
             _ptr(bias), _lib.ACT_FN_GELU if input_activation == "gelu" else _lib.ACT_FN_NONE, norm_kind, float(norm_eps), _ptr(norm_weight), mod_ptr, shift_ptr, int(mod_span),
             int(mod_stride), int(bool(round_after_norm)),
             _lib.ACT_FN_NONE, gate_ptr, int(gate_span), int(gate_stride),

@@ -62,6 +62,12 @@ extern "C" {
 #define SQ_WSCALE_CHANNEL_F32 0 /* float  [N]          (reference: checkpoint.py:49-50, runtime.py:89) */
 #define SQ_WSCALE_GROUP_F16 1   /* __half [N, K / 128] (group-128 scheme of the benchmark)             */
 
+/* OR-ed onto wscale_mode of sq_gemm / sq_linear*: `w_packed` is not the packed int4 matrix but the int8 [N, K]
+ * matrix sq_prepack_weights made from it.  The GEMM then loads operand tiles directly and skips its unpack
+ * stage (faster once the GEMM is compute-bound; twice the weight bytes, so not for small M).  Needs
+ * SQ_CODES_EVEN_ODD codes; acc_dump must be null. */
+#define SQ_WEIGHTS_PREPACKED 4
+
 /* Fused activation pre-pass.
  * Replaces the producer kernels quantize_static_per_tensor_stream_kernel (kernels/w4a8/csrc/w4a8.cu:838-881),
  * quantize_dynamic_per_token_kernel (w4a8.cu:693-747), quantize_static_stream_s4_kernel and
@@ -129,6 +135,12 @@ int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, con
 #define SQ_TIMELINE_SLOTS 512
 int sq_gemm_timeline(const void* codes, const void* w_packed, const void* w_scales, const float* row_scales,
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K, long long* timeline, void* stream);
+
+/* Kernel-native weight form, made once at load time from the on-disk / checkpoint format
+ * (uint8 [N, K/2], kernels/w4a8/ops.py:8-14; the deployment loader deployment.py:180-226 keeps that format):
+ * w_tiled is int8 [N, K], every byte 16 w, in the even-odd k order of SQ_CODES_EVEN_ODD
+ * (k, k+2, k+4, k+6, k+1, k+3, k+5, k+7 within each run of 8).  K % 32 == 0, pointers 16-byte aligned. */
+int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled, void* stream);
 
 /* Bytes of scratch one linear needs between sq_prepass and sq_gemm (codes + row scales), 256-byte rounded.
  * Takes the place of the per-call torch::empty of run_static_streams (w4a8.cu:1358-1360). */

@@ -189,6 +189,39 @@ def test_gemm_group_scheme(native, oracle, m, k, n, abits):
             assert rel_fro(out4.cpu(), want_out) < 2e-3
 
 
+@pytest.mark.parametrize("m,k,n", [(300, 3072, 384), (17, 256, 136), (520, 1024, 128), (2048, 1024, 512)])
+@pytest.mark.parametrize("group", [True, False])
+def test_prepacked_weights_give_the_same_bits(native, oracle, m, k, n, group):
+    """sq_prepack_weights turns the packed int4 matrix into the GEMM's operand form (int8 = 16 w, even-odd k);
+    the GEMM on it skips the unpack stage and must return exactly what it returns on the packed form."""
+    gen = torch.Generator().manual_seed(m + k + n)
+    qweight = torch.randint(-8, 8, (n, k), generator=gen, dtype=torch.int8)
+    packed = oracle.pack_signed_int4(qweight).cuda()
+    tiled = native.prepack_weights(packed)
+    assert tiled.dtype == torch.int8 and tiled.shape == (n, k)
+    want = (qweight.view(n, k // 8, 4, 2).permute(0, 1, 3, 2).reshape(n, k).int() * 16).to(torch.int8)
+    assert torch.equal(tiled.cpu(), want)
+    codes = even_odd(torch.randint(-127, 128, (m, k), generator=gen, dtype=torch.int8)).cuda()
+    wscales = ((torch.rand(n, k // 128, generator=gen) * 0.01 + 0.001).half() if group
+               else torch.rand(n, generator=gen) * 0.01 + 0.001).cuda()
+    row_scales = (torch.rand(m, generator=gen) + 0.5).cuda()
+    bias = (torch.randn(n, generator=gen) * 0.01).bfloat16().cuda()
+    for dtype in (torch.bfloat16, torch.float16):
+        b = bias.to(dtype)
+        plain = native.gemm(codes, packed, wscales, row_scales, b, out_dtype=dtype)
+        pre = native.gemm(codes, tiled, wscales, row_scales, b, out_dtype=dtype)
+        assert torch.equal(pre, plain)
+    with pytest.raises(RuntimeError, match="enum"):  # natural code order does not match the stored k order
+        native.gemm(codes, tiled, wscales, row_scales, None, out_dtype=torch.bfloat16, codes_layout=0)
+    with pytest.raises(RuntimeError, match="enum"):
+        native.gemm(codes, tiled, wscales, row_scales, None, out_dtype=torch.bfloat16, want_accumulators=True)
+    x = (torch.randn(m, k, generator=gen) * 1.5).bfloat16().cuda()
+    if group:
+        signs = oracle.rht_signs(k, seed=1, module_name="s").cuda()
+        assert torch.equal(native.linear(x, tiled, wscales, bias, abits=4, mode="token", signs=signs),
+                           native.linear(x, packed, wscales, bias, abits=4, mode="token", signs=signs))
+
+
 @pytest.mark.parametrize("code,weight,int4_range", [(-128, -8, False), (127, -8, False), (-128, 7, False),
                                                     (127, 7, False), (-8, -8, True), (7, -8, True), (-8, 7, True)])
 def test_gemm_group_extreme_sums(native, oracle, code, weight, int4_range):
