@@ -88,6 +88,7 @@ struct TcParams {
   int ch_tiles, tok_tiles, k_blocks;
   int tok_tile;   // tokens per tile at run time: a multiple of 16, <= TOK
   int slice_cols;  // token columns per drain warp: drain warp j of a lane quarter owns [j, j + 1) * slice_cols
+  int mma_split;        // channel form: 2 when both issuers have K blocks to take (k_blocks >= 2), else 1
   int offset_steps;     // group mode: constant-tile MMAs in front of every group (1 or 4)
   uint32_t offset_word;  // four copies of the constant tile's byte
   uint32_t offset_bits;  // what those MMAs add to every accumulator element
@@ -165,7 +166,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   constexpr int kCols = TOK / 4 < 16 ? 16 : TOK / 4;  // 32 or 16 columns per drain warp
   // TMEM holds a ring of four accumulators so the MMA warp can run ahead of the drain by three groups
   constexpr uint32_t kAccBufs = 4;
-  constexpr int kMmaWarps = kGroup ? 3 : 1;
+  // Channel form: two issuers take alternate K blocks into private accumulators (buffers 2j, 2j + 1 of tile
+  // parity j) that the drain adds; one warp's wait / fence / commit round trips per K block (about 570 cycles
+  // against 256 of tensor-pipe time) would otherwise bound the kernel.
+  constexpr int kMmaWarps = kGroup ? 3 : 2;
   constexpr uint32_t kBufStride = 128;  // TMEM columns between accumulators
   constexpr uint32_t kTmemCols = 512;
   static_assert(TOK == 128 || TOK == 64 || TOK == 32, "tile capacities");
@@ -286,7 +290,14 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             it += blocks_per_group;
             continue;
           }
-          const uint32_t buf = git % kAccBufs, aphase = (git / kAccBufs) & 1u;
+          const uint32_t split = kGroup ? 1u : static_cast<uint32_t>(p.mma_split);
+          if (!kGroup && mine >= split) {
+            it += blocks_per_group;
+            continue;
+          }
+          // channel form: tile parity picks the buffer pair, the issuer its half of it
+          const uint32_t buf = kGroup ? git % kAccBufs : (git & 1u) * 2u + mine;
+          const uint32_t aphase = kGroup ? (git / kAccBufs) & 1u : (git >> 1) & 1u;
           if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9002);
             ok = false;
@@ -304,6 +315,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             __syncwarp();
           }
           for (int kb = 0; kb < blocks_per_group; ++kb, ++it) {
+            if (!kGroup && static_cast<uint32_t>(kb) % split != mine) continue;  // the other issuer's block
             const uint32_t s = it % S, phase = (it / S) & 1u;
             if (!mbar_wait_bounded(bar_wfull + 8 * s, phase, abort_flag, kWaitLimitNs)) {
               if (lane == 0) report_timeout(p.status, abort_flag, 9003);
@@ -317,12 +329,14 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
 #pragma unroll
               for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                const uint32_t accumulate = (kGroup || kb > 0 || k > 0) ? 1u : 0u;
+                const uint32_t accumulate = (kGroup || static_cast<uint32_t>(kb) >= split || k > 0) ? 1u : 0u;
                 // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in the (address >> 4) field
                 umma_i8(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
               }
               umma_commit(bar_empty + 8 * s);  // frees the stage when these MMAs retire
-              if (kb + 1 == blocks_per_group) umma_commit(bar_acc_full + 8 * buf);
+              // after this issuer's last block of the accumulator
+              if (static_cast<uint32_t>(kb) + split >= static_cast<uint32_t>(blocks_per_group))
+                umma_commit(bar_acc_full + 8 * buf);
             }
             __syncwarp();
           }
@@ -436,7 +450,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       }
 
       for (int g = 0; g < groups && ok; ++g, ++git) {
-        const uint32_t buf = git % kAccBufs, aphase = (git / kAccBufs) & 1u;
+        // channel form: the tile's accumulator pair (2j, 2j + 1), the second in use when the issuers split K
+        const uint32_t buf = kGroup ? git % kAccBufs : (git & 1u) * 2u;
+        const uint32_t aphase = kGroup ? (git / kAccBufs) & 1u : (git >> 1) & 1u;
+        const bool split = !kGroup && p.mma_split == 2;
         float scale = 0.0625f;  // the unpacked weights are 16 x the int4 value
         if (kGroup) {
           scale = __half2float(__ushort_as_half(raw0)) * kScaleUp;
@@ -450,18 +467,34 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           ok = false;
           break;
         }
+        if (split && !mbar_wait_bounded(bar_acc_full + 8 * (buf + 1), aphase, abort_flag, kWaitLimitNs)) {
+          if (lane == 0) report_timeout(p.status, abort_flag, 9005);
+          ok = false;
+          break;
+        }
         tc_fence_after_sync();
         if (threadIdx.x == 256) stamp(kTrDrainStart, git);
         uint32_t r[kCols];
         const uint32_t taddr = tmem_base + lane_addr + buf * kBufStride + my_col0;
         if (my_cols > 0) {
           tmem_ld_chunk(taddr, r);
-          tmem_wait_ld();
+          if (split) {
+            uint32_t other[kCols];
+            tmem_ld_chunk(taddr + kBufStride, other);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) r[i] += other[i];  // exact: int32 partial sums of disjoint K blocks
+          } else {
+            tmem_wait_ld();
+          }
         }
         // the accumulator is in registers: give it back before doing the arithmetic
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+        if (lane == 0) {
+          mbar_arrive(bar_acc_empty + 8 * buf);
+          if (!kGroup) mbar_arrive(bar_acc_empty + 8 * (buf + 1));  // kept in step even when unused
+        }
         if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
         if (my_cols > 0) {
           const uint64_t scale2 = pack2(scale, scale);
@@ -643,6 +676,7 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
     const int cap = TOK / 4 < 16 ? 16 : TOK / 4;
     const int want = ((tok_tile + 63) / 64) * 16;
     p.slice_cols = want < cap ? want : cap;
+    p.mma_split = (a.K + kBlockK - 1) / kBlockK >= 2 ? 2 : 1;
     if (a.codes_int4_range) {
       p.offset_steps = 1; p.offset_word = 0x40404040u; p.offset_bits = 1u << 17;
     } else {

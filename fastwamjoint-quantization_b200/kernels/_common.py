@@ -19,7 +19,10 @@ def check_common(tag: str, alignment: int, x, packed, scales, bias, inverse):
     if packed.ndim != 2:
         raise ValueError("Packed WAM weights must be a two-dimensional tensor.")
     k, n = x.shape[-1], packed.shape[0]
-    if packed.dtype != torch.uint8 or packed.shape != (n, k // 2) or k % alignment or n % 8:
+    # uint8 [N, K/2]: the checkpoint format; int8 [N, K]: the same weights after native.prepack_weights
+    form_ok = ((packed.dtype == torch.uint8 and packed.shape == (n, k // 2))
+               or (packed.dtype == torch.int8 and packed.shape == (n, k)))
+    if not form_ok or k % alignment or n % 8:
         raise ValueError(f"Unsupported FastWAM {tag} shape: K={k}, N={n}.")
     if packed.device != x.device or scales.device != x.device:
         raise ValueError("Packed weights and scales must be on the input device.")

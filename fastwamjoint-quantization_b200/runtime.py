@@ -158,6 +158,20 @@ class WAMQuantLinear(nn.Module):
             raise RuntimeError(f"WAM {what} stream names differ from {self.site.module_name}: {layout.names}.")
         return layout
 
+    def prepack(self) -> "WAMQuantLinear":
+        """Native backends: keep a second copy of the weight in the GEMM's operand form (int8 [N, K],
+        ``sq_prepack_weights``), made from the packed checkpoint-format buffer, which stays as it is
+        (deployment files keep their v1 format, ``deployment.py:180-226``).  The GEMM then skips its unpack
+        stage.  Call after the module is on its GPU."""
+        if self.backend != "reference" and self.weight.is_cuda:
+            from . import native
+            self._weight_tiled = native.prepack_weights(self.weight.contiguous())
+        return self
+
+    def _native_weight(self) -> torch.Tensor:
+        tiled = getattr(self, "_weight_tiled", None)
+        return self.weight if tiled is None or tiled.device != self.weight.device else tiled
+
     def _call(self, x: torch.Tensor):
         """The active call for a native launch: the Python index, or - when the state is ``on_device`` - the
         state's device tensor, which the kernels read when they run (one graph for all calls)."""
@@ -171,7 +185,7 @@ class WAMQuantLinear(nn.Module):
         layout = self._layout(x, "checkpoint")
         if self.backend != "reference":
             call = self._call(x)
-            args = (x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges,
+            args = (x, self._native_weight(), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges,
                     self.gamma_gains, layout.token_counts, call)
             if self.input_rotation_signs is not None:
                 return self._native_ops.symmetric_scheduled_stream_rht_linear(
@@ -203,7 +217,7 @@ class WAMQuantLinear(nn.Module):
             raise RuntimeError("WAM AdaLN block fusion was not enabled for this site.")
         layout = self._layout(x, "fused AdaLN")
         return self._native_ops.symmetric_scheduled_stream_adaln_linear(
-            x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
+            x, self._native_weight(), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
             layout.token_counts, self._call(x), scale, shift, epsilon)
 
     def forward_gate_residual(self, x, residual, gate):
@@ -211,7 +225,7 @@ class WAMQuantLinear(nn.Module):
             raise RuntimeError("WAM gate/residual block fusion was not enabled for this site.")
         layout = self._layout(x, "fused residual")
         return self._native_ops.symmetric_scheduled_stream_gate_residual_linear(
-            x, self.weight, self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
+            x, self._native_weight(), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
             layout.token_counts, self._call(x), residual, gate)
 
 
@@ -234,8 +248,9 @@ def set_wam_block_fusions(model: nn.Module, enabled: bool) -> int:
 
 def apply_checkpoint(model: nn.Module, checkpoint, *, state: DenoiseCallState | None = None,
                      backend: Literal["reference", "cutlass_w4a8", "cutlass_w4a4"] = "reference",
-                     fuse_block: bool = False):
-    """Replace every site's ``nn.Linear`` by a ``WAMQuantLinear`` (``runtime.py:226-276``).  ``checkpoint``
+                     fuse_block: bool = False, prepack: bool = False):
+    """Replace every site's ``nn.Linear`` by a ``WAMQuantLinear`` (``runtime.py:226-276``).  ``prepack`` also
+    gives every native site on a GPU its kernel-native weight copy (``WAMQuantLinear.prepack``).  ``checkpoint``
     needs ``validate()``, ``sites``, ``weight_bits``, ``activation_bits``, ``num_calls`` and
     ``stream_config`` like the reference's ``QuantizationCheckpoint``.  All sites are validated before the
     first replacement; replacement is one site at a time so no second copy of the model exists."""
@@ -267,5 +282,7 @@ def apply_checkpoint(model: nn.Module, checkpoint, *, state: DenoiseCallState | 
                                      weight_bits=checkpoint.weight_bits, activation_bits=checkpoint.activation_bits,
                                      backend=backend, fuse_block=fuse_block).to(module.weight.device)
         replacement.train(module.training)
+        if prepack:
+            replacement.prepack()
         setattr(parent, child, replacement)
     return state, len(checkpoint.sites)

@@ -256,6 +256,23 @@ def test_live_graph_capture_replay_and_refusals(m):
     assert not hasattr(model, "_rollout_graph")
 
 
+@pytest.mark.parametrize("abits", [8, 4])
+def test_module_prepack_keeps_every_bit(m, abits):
+    """``WAMQuantLinear.prepack()`` switches the GEMM to the kernel-native weight copy: same outputs bit for
+    bit, the packed checkpoint-format buffer untouched, the fused entries included."""
+    R = m["runtime"]
+    torch.manual_seed(3)
+    source = torch.nn.Linear(256, 64, bias=True, device="cuda", dtype=torch.bfloat16)
+    state = m["state"].DenoiseCallState(2)
+    layer = R.WAMQuantLinear(source, _entry(m, False, n=64), state=state, stream_config=m["streams"].FastWAMStreamConfig(),
+                             weight_bits=4, activation_bits=abits, backend=f"cutlass_w4a{abits}")
+    x = torch.randn(1, 32, 256, device="cuda", dtype=torch.bfloat16)
+    state.set(1)
+    before, packed_before = layer(x), layer.weight.clone()
+    assert layer.prepack() is layer and layer._native_weight().dtype == torch.int8
+    assert torch.equal(layer(x), before) and torch.equal(layer.weight, packed_before)
+
+
 def test_single_graph_for_all_calls(m):
     """One captured graph replayed at every call index: the linears read the index from device memory, so the
     outputs equal the per-call eager results bit for bit, one capture exists, and every index was validated once."""
