@@ -36,7 +36,7 @@ WORKLOADS = {
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch from the committed ncu capture
 # (profiles/sq_gemm_tc_kernel_c2_w4a4_rht.md); other workloads have no capture
-NCU_TRAFFIC_BYTES = {("c2", "packed"): 11.26e6}
+NCU_TRAFFIC_BYTES = {("c2", "packed"): 11.26e6, ("c2", "prepacked"): 15.97e6}
 
 
 def algorithmic_bytes(m, k, n, rotate, weights="packed"):

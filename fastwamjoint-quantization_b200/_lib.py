@@ -35,6 +35,7 @@ _SIGNATURES = {
     "sq_gemm_timeline": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                  c_void_p, c_void_p]),
     "sq_prepack_weights": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "sq_mma_rate": (c_int, [c_int, c_int, c_void_p, c_void_p]),
     "sq_workspace_bytes": (c_size_t, [c_int64, c_int64]),
     "sq_linear": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -238,6 +238,10 @@ int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled
                                     static_cast<cudaStream_t>(stream));
 }
 
+int sq_mma_rate(int n_cols, int iterations, long long* cycles, void* stream) {
+  return sq::launch_mma_rate(n_cols, iterations, cycles, static_cast<cudaStream_t>(stream));
+}
+
 size_t sq_workspace_bytes(int64_t M, int64_t K) {
   if (M < 0 || K < 0) return 0;
   return sq::round256(static_cast<size_t>(M) * static_cast<size_t>(K)) + sq::round256(static_cast<size_t>(M) * 4u);
@@ -412,6 +416,7 @@ const char* sq_status_string(int status) {
     case SQ_ERR_WORKSPACE: return "workspace too small";
     case SQ_ERR_DEVICE_WAIT: return "a kernel gave up a bounded wait";
     case SQ_ERR_SCRATCH_LIMIT: return "rows * K is beyond the library-owned scratch of sq_linear_noalloc";
+    case 9006: return "device: the MMA rate probe timed out waiting for its MMAs";
     case 9001: return "device: TMA producer timed out waiting for a free stage";
     case 9002: return "device: MMA warp timed out waiting for a free accumulator";
     case 9003: return "device: MMA warp timed out waiting for operands";

@@ -721,7 +721,84 @@ int launch_mode(const GemmArgs& a, cudaStream_t stream) {
   return launch_tok<128, kGroup>(a, t, stream);
 }
 
+// ---------------------------------------------------------------------------------- tensor-pipe rate probe
+// One warp per SM issues `iters` x 4 kind::i8 MMAs (M = 128, N = kN, K = 32) back to back on fixed shared-memory
+// tiles, commits once and waits (bounded); thread block 0 reports the SM cycles from first issue to completion.
+template <int kN>
+__global__ void __launch_bounds__(128, 1) sq_mma_rate_kernel(long long* cycles, int iters, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_tile = base;                   // 128 rows x 128 B
+  const uint32_t b_tile = base + kWBytes;         // kN rows x 128 B
+  const uint32_t bar = b_tile + kN * kBlockK;
+  const uint32_t slot = bar + 16;
+  const uint32_t abort_slot = slot + 4;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + (abort_slot - base));
+  for (uint32_t i = threadIdx.x; i < (kWBytes + kN * kBlockK) / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(gen)[i] = 0x01010101u;
+  fence_proxy_async_smem();
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    tmem_alloc(slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(gen + (slot - base));
+  if (warp == 0) {
+    const uint32_t idesc = umma_idesc_i8(kBlockCh, kN);
+    const uint64_t desc_a = umma_desc_k128(a_tile), desc_b = umma_desc_k128(b_tile);
+    const long long t0 = clock64();
+    if (elect_one()) {
+      for (int it = 0; it < iters; ++it) {
+        const uint32_t d = tmem + (it & 1) * 256;
+#pragma unroll
+        for (int k = 0; k < kBlockK / kUmmaK; ++k) umma_i8(d, desc_a + 2 * k, desc_b + 2 * k, idesc, k > 0 ? 1u : 0u);
+      }
+      umma_commit(bar);
+    }
+    __syncwarp();
+    if (!mbar_wait_bounded(bar, 0, abort_flag, kWaitLimitNs) && threadIdx.x == 0) report_timeout(status, abort_flag, 9006);
+    const long long t1 = clock64();
+    if (threadIdx.x == 0 && blockIdx.x == 0) cycles[0] = t1 - t0;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int kN>
+int launch_mma_rate_n(long long* cycles, int iters, cudaStream_t stream) {
+  const int smem = static_cast<int>(kWBytes) + kN * kBlockK + 2048;
+  cudaError_t err = cudaFuncSetAttribute(sq_mma_rate_kernel<kN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  sq_mma_rate_kernel<kN><<<sm_count(), 128, smem, stream>>>(cycles, iters, device_status_word());
+  err = cudaGetLastError();
+  return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
+}
+
 }  // namespace
+
+int launch_mma_rate(int n_cols, int iters, long long* cycles, cudaStream_t stream) {
+  if (cycles == nullptr) return SQ_ERR_NULL;
+  if (iters <= 0 || iters > 100000) return SQ_ERR_SHAPE;
+  switch (n_cols) {
+    case 64: return launch_mma_rate_n<64>(cycles, iters, stream);
+    case 128: return launch_mma_rate_n<128>(cycles, iters, stream);
+    case 256: return launch_mma_rate_n<256>(cycles, iters, stream);
+    default: return SQ_ERR_ENUM;
+  }
+}
 
 int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t stream) {
   int v = validate_gemm(a);

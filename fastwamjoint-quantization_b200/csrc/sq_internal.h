@@ -64,6 +64,9 @@ int launch_gemm_check(const GemmArgs& a, cudaStream_t stream);
 // Group-scale bf16 GEMM with M > 128 only: same result, plus clock stamps of CTA 0's pipeline roles.
 int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t stream);
 
+// Tensor-pipe rate probe: n_cols in {64, 128, 256}; cycles is a device int64.
+int launch_mma_rate(int n_cols, int iters, long long* cycles, cudaStream_t stream);
+
 // Device-side status word (0 = fine).  Written by kernels that gave up a bounded wait.
 int* device_status_word();
 

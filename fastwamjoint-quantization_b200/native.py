@@ -237,6 +237,16 @@ def gemm_timeline(codes, packed, w_scales, row_scales, bias):
     return out, stamps
 
 
+def mma_rate(n_cols: int = 128, iterations: int = 2000) -> float:
+    """SM cycles the tensor pipe takes per ``kind::i8`` MMA of M = 128, N = ``n_cols``, K = 32 when one thread
+    issues them back to back (``sq_mma_rate``; synchronises)."""
+    cycles = torch.zeros(1, device="cuda", dtype=torch.int64)
+    status = _lib.load_library().sq_mma_rate(int(n_cols), int(iterations), cycles.data_ptr(), _stream())
+    _lib.check(status, "sq_mma_rate")
+    torch.cuda.synchronize()
+    return cycles.item() / (4.0 * iterations)
+
+
 def device_status() -> int:
     """Read and clear the device-side status word (synchronises)."""
     return int(_lib.load_library().sq_device_status())

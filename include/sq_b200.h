@@ -142,6 +142,12 @@ int sq_gemm_timeline(const void* codes, const void* w_packed, const void* w_scal
  * (k, k+2, k+4, k+6, k+1, k+3, k+5, k+7 within each run of 8).  K % 32 == 0, pointers 16-byte aligned. */
 int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled, void* stream);
 
+/* Profiling aid with no counterpart in the reference: one warp per SM issues `iterations` x 4
+ * tcgen05.mma.kind::i8 (M = 128, N = n_cols in {64, 128, 256}, K = 32) back to back on fixed shared-memory tiles
+ * and waits for them; `cycles` (device int64) receives thread block 0's SM cycles from first issue to
+ * completion, so cycles / (4 * iterations) is the tensor pipe's time per MMA of that shape. */
+int sq_mma_rate(int n_cols, int iterations, long long* cycles, void* stream);
+
 /* Bytes of scratch one linear needs between sq_prepass and sq_gemm (codes + row scales), 256-byte rounded.
  * Takes the place of the per-call torch::empty of run_static_streams (w4a8.cu:1358-1360). */
 size_t sq_workspace_bytes(int64_t M, int64_t K);

@@ -301,6 +301,17 @@ def test_linear_graph_capture_and_replay_after_mutation(native, oracle):
     assert torch.equal(captured, run())
 
 
+def test_mma_rate_probe(native):
+    """The tensor-pipe probe runs, finishes (bounded wait, status 0) and reports a plausible time per MMA:
+    at least the 32 cycles a K = 32 step of 128 x 64 would take at twice the nominal rate, at most 1000."""
+    for n_cols in (64, 128, 256):
+        cycles = native.mma_rate(n_cols, 500)
+        assert 32.0 <= cycles <= 1000.0, (n_cols, cycles)
+    assert native.device_status() == 0
+    with pytest.raises(RuntimeError, match="enum"):
+        native.mma_rate(96, 10)
+
+
 def test_rejected_calls_raise(native, oracle):
     case = oracle.prepare_token_linear(8, 256, 16, abits=8, seed=0)
     packed = oracle.pack_signed_int4(case["qweight"]).cuda()
