@@ -609,7 +609,7 @@ def main():
                     "pipeline": "host->device copy, linear and device->host copy of consecutive steps overlap (3 streams, 2 buffers)"},
             "roofline": roofline, "clocks": clocks, "parity_rel_fro": err,
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:  # reported at N = 1 only: the other ranks would share the cores
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
             median, repeats = time_cpu(cpu_forward_factory(oracle, case))

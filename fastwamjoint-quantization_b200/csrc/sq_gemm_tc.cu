@@ -43,6 +43,10 @@ constexpr int kBlockCh = 128;  // output channels per tile = UMMA M = TMEM lanes
 constexpr int kBlockK = 128;   // int8 K elements per stage = one swizzle row = one weight group
 constexpr int kUmmaK = 32;     // K of one kind::i8 instruction
 constexpr int kThreads = 768;  // 4 control + 4 unpack + 16 drain warps
+// Register targets per role after setmaxnreg (control 32, unpack 48, drain 96).  setmaxnreg.inc only hands out
+// registers the CTA was launched with and waits for ever when the targets add up to more, so the launcher
+// checks this sum against (registers per thread at launch) x kThreads before every launch.
+constexpr int kRegisterPoolNeeded = 4 * 32 * 32 + 4 * 32 * 48 + 16 * 32 * 96;
 constexpr uint32_t kPackedBytes = kBlockCh * kBlockK / 2;  // 8 KiB
 constexpr uint32_t kWBytes = kBlockCh * kBlockK;           // 16 KiB
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
@@ -690,6 +694,17 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   p.gate_row_stride = a.gate_row_stride; p.residual = a.residual;
   const int tiles = p.ch_tiles * p.tok_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();
+  {  // never launch a register split the CTA cannot satisfy
+    static int launch_regs[64] = {0};
+    if (dev >= 0 && dev < 64 && launch_regs[dev] == 0) {
+      cudaFuncAttributes attr;
+      const cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      launch_regs[dev] = attr.numRegs;
+    }
+    const int regs = (dev >= 0 && dev < 64) ? launch_regs[dev] : 0;
+    if (regs * kThreads < kRegisterPoolNeeded) return SQ_ERR_DRIVER;
+  }
   kernel<<<grid, kThreads, smem, stream>>>(tmap_codes, tmap_packed, p);
   cudaError_t err = cudaGetLastError();
   return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
