@@ -107,6 +107,47 @@ struct PrepassParams {
 
 constexpr float kRoundMagic = 12582912.0f;  // 1.5 * 2^23
 
+// Packed single-precision arithmetic (two IEEE operations per instruction, each rounded to nearest even exactly
+// like its scalar form): the pre-pass is bound by the instructions it issues, and most of its arithmetic applies
+// the same operation to neighbouring elements.
+#define SQ_PACK2(dst, lo, hi) "mov.b64 " dst ", {" lo ", " hi "};\n\t"
+// (a0, a1) = (a0, a1) * (b0, b1)
+__device__ __forceinline__ void mul2(float& a0, float& a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 a, b;\n\t" SQ_PACK2("a", "%0", "%1") SQ_PACK2("b", "%2", "%3")
+      "mul.rn.f32x2 a, a, b;\n\tmov.b64 {%0, %1}, a;\n\t}\n"
+      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+// (a0, a1) = (a0, a1) + (b0, b1)
+__device__ __forceinline__ void add2(float& a0, float& a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 a, b;\n\t" SQ_PACK2("a", "%0", "%1") SQ_PACK2("b", "%2", "%3")
+      "add.rn.f32x2 a, a, b;\n\tmov.b64 {%0, %1}, a;\n\t}\n"
+      : "+f"(a0), "+f"(a1) : "f"(b0), "f"(b1));
+}
+// butterfly on two pairs: (a, b) -> (a + b, a - b)
+__device__ __forceinline__ void butterfly2(float& a0, float& a1, float& b0, float& b1) {
+  asm("{\n\t.reg .b64 a, b, s, d;\n\t" SQ_PACK2("a", "%0", "%1") SQ_PACK2("b", "%2", "%3")
+      "add.rn.f32x2 s, a, b;\n\tsub.rn.f32x2 d, a, b;\n\t"
+      "mov.b64 {%0, %1}, s;\n\tmov.b64 {%2, %3}, d;\n\t}\n"
+      : "+f"(a0), "+f"(a1), "+f"(b0), "+f"(b1));
+}
+// (a0, a1) = (a0, a1) * (m, m) + (c0, c1)
+__device__ __forceinline__ void fma2s(float& a0, float& a1, float m, float c0, float c1) {
+  asm("{\n\t.reg .b64 a, b, c;\n\t" SQ_PACK2("a", "%0", "%1") SQ_PACK2("b", "%2", "%2") SQ_PACK2("c", "%3", "%4")
+      "fma.rn.f32x2 a, a, b, c;\n\tmov.b64 {%0, %1}, a;\n\t}\n"
+      : "+f"(a0), "+f"(a1) : "f"(m), "f"(c0), "f"(c1));
+}
+// correctly rounded (x0, x1) / divisor from reciprocal = RN(1 / divisor): q0 = x r, two residual corrections
+__device__ __forceinline__ void divide2(float& x0, float& x1, float divisor, float reciprocal) {
+  asm("{\n\t.reg .b64 x, r, nd, q, t;\n\t.reg .f32 negd;\n\t"
+      SQ_PACK2("x", "%0", "%1") SQ_PACK2("r", "%3", "%3")
+      "neg.f32 negd, %2;\n\t" SQ_PACK2("nd", "negd", "negd")
+      "mul.rn.f32x2 q, x, r;\n\t"
+      "fma.rn.f32x2 t, q, nd, x;\n\tfma.rn.f32x2 q, t, r, q;\n\t"
+      "fma.rn.f32x2 t, q, nd, x;\n\tfma.rn.f32x2 q, t, r, q;\n\t"
+      "mov.b64 {%0, %1}, q;\n\t}\n"
+      : "+f"(x0), "+f"(x1) : "f"(divisor), "f"(reciprocal));
+}
+
 // clamp to [-qmax, qmax], round to nearest even; the code is the low byte of the result
 __device__ __forceinline__ uint32_t round_code(float q, float qmax) {
   return __float_as_uint(__fadd_rn(fminf(fmaxf(q, -qmax), qmax), kRoundMagic));
@@ -224,21 +265,21 @@ __global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepas
       if (vec < vectors) {
         const float4 s0 = __ldg(reinterpret_cast<const float4*>(p.signs) + 2 * vec);
         const float4 s1 = __ldg(reinterpret_cast<const float4*>(p.signs) + 2 * vec + 1);
-        v[j][0] *= s0.x; v[j][1] *= s0.y; v[j][2] *= s0.z; v[j][3] *= s0.w;
-        v[j][4] *= s1.x; v[j][5] *= s1.y; v[j][6] *= s1.z; v[j][7] *= s1.w;
+        mul2(v[j][0], v[j][1], s0.x, s0.y); mul2(v[j][2], v[j][3], s0.z, s0.w);
+        mul2(v[j][4], v[j][5], s1.x, s1.y); mul2(v[j][6], v[j][7], s1.z, s1.w);
       }
-      // strides 1, 2, 4 inside the thread
+      // stride 1 inside the thread (the two halves of a pair meet: scalar)
 #pragma unroll
-      for (int stride = 1; stride < 8; stride <<= 1) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if ((i & stride) == 0) {
-            const float left = v[j][i], right = v[j][i + stride];
-            v[j][i] = left + right;
-            v[j][i + stride] = left - right;
-          }
-        }
+      for (int i = 0; i < 8; i += 2) {
+        const float left = v[j][i], right = v[j][i + 1];
+        v[j][i] = left + right;
+        v[j][i + 1] = left - right;
       }
+      // strides 2 and 4 inside the thread: whole pairs meet
+      butterfly2(v[j][0], v[j][1], v[j][2], v[j][3]);
+      butterfly2(v[j][4], v[j][5], v[j][6], v[j][7]);
+      butterfly2(v[j][0], v[j][1], v[j][4], v[j][5]);
+      butterfly2(v[j][2], v[j][3], v[j][6], v[j][7]);
       // strides 8, 16, ... across lanes: the lane whose bit is clear holds "left"
 #pragma unroll
       for (int stage = 0; stage < 5; ++stage) {  // blocks of up to 256 = 32 lanes x 8
@@ -247,17 +288,17 @@ __global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepas
           const int lane_bit = kOne << stage;
           const float mine = (threadIdx.x & lane_bit) != 0 ? -1.0f : 1.0f;  // right: other - v, left: v + other
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j][i], lane_bit);
-            v[j][i] = fmaf(v[j][i], mine, other);
+          for (int i = 0; i < 8; i += 2) {
+            const float other0 = __shfl_xor_sync(0xffffffffu, v[j][i], lane_bit);
+            const float other1 = __shfl_xor_sync(0xffffffffu, v[j][i + 1], lane_bit);
+            fma2s(v[j][i], v[j][i + 1], mine, other0, other1);
           }
         }
       }
       if (!kMix) {
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
-          v[j][i] = __fmul_rn(v[j][i], p.rht_norm);
-          v[j][i + 1] = __fmul_rn(v[j][i + 1], p.rht_norm);
+          mul2(v[j][i], v[j][i + 1], p.rht_norm, p.rht_norm);
           Vec8<T>::round_trip2(v[j][i], v[j][i + 1]);
         }
       }
@@ -345,8 +386,8 @@ __global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepas
       if (vec < vectors) {
         const float4 d0 = __ldg(reinterpret_cast<const float4*>(p.inv_d) + 2 * vec);
         const float4 d1 = __ldg(reinterpret_cast<const float4*>(p.inv_d) + 2 * vec + 1);
-        v[j][0] *= d0.x; v[j][1] *= d0.y; v[j][2] *= d0.z; v[j][3] *= d0.w;
-        v[j][4] *= d1.x; v[j][5] *= d1.y; v[j][6] *= d1.z; v[j][7] *= d1.w;
+        mul2(v[j][0], v[j][1], d0.x, d0.y); mul2(v[j][2], v[j][3], d0.z, d0.w);
+        mul2(v[j][4], v[j][5], d1.x, d1.y); mul2(v[j][6], v[j][7], d1.z, d1.w);
       }
     }
   }
@@ -404,13 +445,13 @@ __global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepas
     uint32_t q[8];  // code in the low byte
     if (p.mode == SQ_ACT_TOKEN) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float x = v[j][i];
-        const float q0 = __fmul_rn(x, reciprocal);
-        const float q1 = fmaf(fmaf(-q0, divisor, x), reciprocal, q0);
-        const float q2 = fmaf(fmaf(-q1, divisor, x), reciprocal, q1);
-        // no clamp: |x| <= amax and divisor >= RN(amax / qmax) give |q2| <= qmax (1 + 2^-23), which rounds to qmax
-        q[i] = __float_as_uint(__fadd_rn(q2, kRoundMagic));
+      for (int i = 0; i < 8; i += 2) {
+        float q0 = v[j][i], q1 = v[j][i + 1];
+        divide2(q0, q1, divisor, reciprocal);
+        // no clamp: |x| <= amax and divisor >= RN(amax / qmax) give |q| <= qmax (1 + 2^-23), which rounds to qmax
+        add2(q0, q1, kRoundMagic, kRoundMagic);
+        q[i] = __float_as_uint(q0);
+        q[i + 1] = __float_as_uint(q1);
       }
     } else {
 #pragma unroll
