@@ -9,10 +9,12 @@
 //   warp 0        TMA producer: per 128-K block one box of packed int4 weights [128 ch x 64 B] and one
 //                 box of int8 activation codes [tokens x 128 B, 128-byte swizzle]
 //   warps 1-3     issue tcgen05.mma.kind::i8 (4 x K=32 per block) and commit to mbarriers; in the group form
-//                 they take the groups round-robin, in the channel form warp 1 works alone.  Warp 1 owns TMEM.
+//                 they take the groups round-robin, in the channel form warps 1 and 2 take alternate K blocks
+//                 into private accumulators that the drain adds.  Warp 1 owns TMEM.
 //   warps 4-7     unpack int4 -> int8 from the packed stage into the canonical K-major 128B-swizzled
 //                 operand tile (nibble v becomes the int8 value 16 v; the factor 1/16 is exact and is
-//                 folded into the scale)
+//                 folded into the scale).  With prepacked weights (kPre) the producer loads that tile itself
+//                 and these warps have nothing to do.
 //   warps 8-23    drain, four warps per TMEM lane quarter, each owning a slice of the token columns:
 //                 tcgen05.ld the int32 accumulator of one weight group, hand the accumulator back, fold it
 //                 into fp32 sums in registers with the group scale; after the last group apply the row
