@@ -190,3 +190,28 @@ def test_weight_helpers_match_oracle(mods, oracle, golden):
     assert torch.equal(H.randomized_block_hadamard_transform(golden["rot_in"], golden["rot_signs"]), golden["rot_rht_out"])
     v, scale = golden["fq_in"], golden["fq_a4_scale"]
     assert torch.equal(Q.symmetric_fake_quant(v, bits=4, scale=scale), golden["fq_a4_out"])
+
+
+def test_composite_rotation_helper_matches_the_reference(mods, golden):
+    """``rht.randomized_composite_hadamard_transform`` with the reference's own sign matrices against the
+    reference's "rht" transform at widths 3072 and 14336 (recorded vectors), bit for bit on the CPU."""
+    H = mods["rht"]
+    assert H.composite_order(3072) == 12 and H.composite_order(14336) == 28 and H.composite_order(4096) is None
+    for order, width in ((12, 3072), (28, 14336)):
+        signs = H.rht_signs(width, seed=42, module_name="linear")
+        matrix = golden[f"mix{order}_matrix"].float()
+        got = H.randomized_composite_hadamard_transform(golden[f"mix{order}_in"], signs, matrix)
+        assert torch.equal(got, golden[f"mix{order}_out"])
+    with pytest.raises(ValueError):
+        H.composite_hadamard(torch.zeros(2, 3072), torch.ones(28, 28))
+    with pytest.raises(ValueError):
+        H.randomized_composite_hadamard_transform(torch.zeros(2, 96), torch.ones(95), torch.ones(12, 12))
+
+
+def test_call_state_device_mode_defaults(mods):
+    """The device-side call index is opt-in: a fresh state is host-indexed and keeps no device tensors."""
+    state = mods["state"].DenoiseCallState(4)
+    assert state.on_device is False and state._mirrors == {}
+    state.set(2)
+    assert state.require() == 2
+    assert mods["state"].DenoiseCallState(4) == mods["state"].DenoiseCallState(4)
