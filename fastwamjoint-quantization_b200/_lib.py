@@ -56,7 +56,7 @@ _SIGNATURES = {
                                      c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p]),
     "sq_linear_composite": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p,
-                                    c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                    c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "sq_linear_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,

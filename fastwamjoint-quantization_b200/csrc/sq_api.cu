@@ -345,20 +345,26 @@ int sq_prepass_composite(const void* x, int x_dtype, int64_t rows, int64_t K, in
 
 int sq_linear_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
                         const float* inv_d, const float* signs, const float* mix, int mix_order,
-                        const float* act_scales, const float* gains, int64_t calls, int64_t call, int64_t span,
-                        int64_t streams, int64_t seq_tokens, const void* w_packed, const void* w_scales,
-                        int wscale_mode, const void* bias, void* out, void* workspace, size_t workspace_bytes,
-                        void* stream) {
+                        const float* act_scales, const float* gains, int64_t calls, int64_t call,
+                        const int32_t* call_index, int64_t span, int64_t streams, int64_t seq_tokens,
+                        const void* w_packed, const void* w_scales, int wscale_mode, const void* bias, void* out,
+                        void* workspace, size_t workspace_bytes, void* stream) {
   if (mix == nullptr || (workspace == nullptr && rows > 0)) return SQ_ERR_NULL;
   if (workspace_bytes < sq_workspace_bytes(rows, K)) return SQ_ERR_WORKSPACE;
   const float* act_scale = nullptr;
   const float* gain_row = nullptr;
   if (mode == SQ_ACT_STATIC) {
     if (act_scales == nullptr || gains == nullptr) return SQ_ERR_NULL;
-    if (calls <= 0 || call < 0 || call >= calls) return SQ_ERR_INDEX;
     if (streams <= 0) return SQ_ERR_SHAPE;
-    act_scale = act_scales + call;
-    gain_row = gains + call * streams;
+    if (call_index != nullptr) {
+      if (calls <= 0) return SQ_ERR_INDEX;
+      act_scale = act_scales;
+      gain_row = gains;
+    } else {
+      if (calls <= 0 || call < 0 || call >= calls) return SQ_ERR_INDEX;
+      act_scale = act_scales + call;
+      gain_row = gains + call * streams;
+    }
   }
   int8_t* codes = static_cast<int8_t*>(workspace);
   float* row_scales = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
@@ -369,9 +375,16 @@ int sq_linear_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int
     const int v = sq::validate_gemm(a);
     if (v != SQ_OK) return v;
   }
-  const int status = sq_prepass_composite(x, x_dtype, rows, K, abits, mode, inv_d, signs, mix, mix_order, act_scale,
-                                          gain_row, span, streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
-                                          stream);
+  sq::PrepassFusion rotation;
+  rotation.mix = mix;
+  rotation.mix_order = mix_order;
+  if (mode == SQ_ACT_STATIC && call_index != nullptr) {
+    rotation.call_index = call_index;
+    rotation.calls = calls;
+  }
+  const int status = sq::launch_prepass(x, x_dtype, rows, K, abits, mode, inv_d, signs, 0, act_scale, gain_row, span,
+                                        streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
+                                        static_cast<cudaStream_t>(stream), &rotation);
   if (status != SQ_OK) return status;
   return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
 }

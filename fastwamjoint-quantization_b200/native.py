@@ -161,10 +161,13 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
         raise RuntimeError("out must be a contiguous tensor of shape x.shape[:-1] + (N,) in x's dtype.")
     group = w_scales.dtype == torch.float16
     calls = 0 if act_scales is None else act_scales.numel()
+    if call_index is not None and (call_index.dtype != torch.int32 or call_index.numel() != 1
+                                   or call_index.device != x.device):
+        raise ValueError("call_index must be a one-element int32 tensor on the input's device.")
     if mix is not None:
         # composite rotation (order x power of two); a rotated site takes no block fusion (runtime.py:75-78)
         if (norm is not None or mod_scale is not None or gate is not None or residual is not None
-                or activation is not None or input_activation is not None or call_index is not None):
+                or activation is not None or input_activation is not None):
             raise ValueError("the composite rotation cannot be combined with fused block work.")
         mix = _mix_matrix(mix, x)
         with torch.cuda.device(x.device):
@@ -172,7 +175,7 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
                 x.data_ptr(), _DTYPES[x.dtype], rows, k, n, int(abits),
                 _lib.ACT_TOKEN if mode == "token" else _lib.ACT_STATIC,
                 _ptr(inverse), _ptr(signs), mix.data_ptr(), int(mix.shape[0]), _ptr(act_scales), _ptr(gains),
-                int(calls), int(call), int(span), int(streams), int(x.shape[-2]),
+                int(calls), int(call), _ptr(call_index), int(span), int(streams), int(x.shape[-2]),
                 packed.data_ptr(), w_scales.data_ptr(), _wscale_mode(packed, w_scales),
                 _ptr(bias), out.data_ptr(), workspace.data_ptr(), nbytes, _stream())
         _lib.check(status, "sq_linear_composite")
@@ -194,9 +197,6 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
         gate_span = rows // gate_rows
     if residual is not None:
         residual = residual.contiguous()
-    if call_index is not None and (call_index.dtype != torch.int32 or call_index.numel() != 1
-                                   or call_index.device != x.device):
-        raise ValueError("call_index must be a one-element int32 tensor on the input's device.")
     with torch.cuda.device(x.device):
         status = lib.sq_linear_scheduled(
             x.data_ptr(), _DTYPES[x.dtype], rows, k, n, int(abits),

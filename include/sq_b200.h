@@ -169,17 +169,18 @@ int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, in
  * out[i * part + c] = (sum_j mix[i, j] * h[j * part + c]) / sqrt(order), rounded to x_dtype; the rest is
  * sq_prepass / sq_linear.  `mix` is float [order, order] with entries +-1 (the caller's Hadamard matrix of that
  * order, device memory), 2 <= order <= 32, K <= 16384.  The sum over j runs in ascending j in fp32, which is
- * not the reference's BLAS order: rotated values agree to fp32 rounding, codes to +-1 on a few in ten thousand. */
+ * not the reference's BLAS order: rotated values agree to fp32 rounding, codes to +-1 on a few in ten thousand.
+ * `call_index` of sq_linear_composite: null, or a device int32 read when the kernel runs (see sq_linear_scheduled). */
 int sq_prepass_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
                          const float* signs, const float* mix, int mix_order, const float* act_scale,
                          const float* gains, int64_t span, int64_t streams, int64_t seq_tokens, int codes_layout,
                          int pack_int4, void* codes, float* row_scales, void* stream);
 int sq_linear_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
                         const float* inv_d, const float* signs, const float* mix, int mix_order,
-                        const float* act_scales, const float* gains, int64_t calls, int64_t call, int64_t span,
-                        int64_t streams, int64_t seq_tokens, const void* w_packed, const void* w_scales,
-                        int wscale_mode, const void* bias, void* out, void* workspace, size_t workspace_bytes,
-                        void* stream);
+                        const float* act_scales, const float* gains, int64_t calls, int64_t call,
+                        const int32_t* call_index, int64_t span, int64_t streams, int64_t seq_tokens,
+                        const void* w_packed, const void* w_scales, int wscale_mode, const void* bias, void* out,
+                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* sq_linear with work of the surrounding block folded into its two kernels.
  * Pre-pass side, replaces quantize_static_adaln_stream_kernel / quantize_dynamic_adaln_per_token_kernel

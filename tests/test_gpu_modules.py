@@ -256,6 +256,28 @@ def test_live_graph_capture_replay_and_refusals(m):
     assert not hasattr(model, "_rollout_graph")
 
 
+def test_composite_rotation_with_device_call_index(m, golden):
+    """The composite-rotation entry reads its schedule entry from device memory too: same bits as the host index."""
+    ops = m["ops4"]
+    gen = torch.Generator().manual_seed(9)
+    rows, k, n, calls = 64, 3072, 256, 3
+    x = (torch.randn(1, rows, k, generator=gen) * 1.5).bfloat16().cuda()
+    packed = m["ops8"].pack_signed_int4(torch.randint(-7, 8, (n, k), generator=gen, dtype=torch.int8)).cuda()
+    scales, inverse = torch.full((n,), 0.002).cuda(), torch.ones(k).cuda()
+    act = torch.linspace(0.3, 0.9, calls).cuda()
+    gains = (torch.rand(calls, 2, generator=gen) + 0.5).cuda()
+    signs = torch.where(torch.rand(k, generator=gen) < 0.5, -1.0, 1.0).cuda()
+    matrix = golden["mix12_matrix"].float().cuda()
+    run = lambda call: ops.symmetric_scheduled_stream_rht_linear(x, packed, scales, None, inverse, act, gains, (32, 32),
+                                                                 call, signs, mix=matrix)
+    host = [run(c) for c in range(calls)]
+    assert not torch.equal(host[0], host[2])
+    index = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for c in (2, 0, 1):
+        index.fill_(c)
+        assert torch.equal(run(index), host[c])
+
+
 @pytest.mark.parametrize("abits", [8, 4])
 def test_module_prepack_keeps_every_bit(m, abits):
     """``WAMQuantLinear.prepack()`` switches the GEMM to the kernel-native weight copy: same outputs bit for
