@@ -160,6 +160,131 @@ def measure_int8_peak(device):
 DIT_WORKLOADS = {"dit_a8": (8, False), "dit_a4": (4, True)}
 
 
+def measured_peaks():
+    """(HBM GB/s, source) from MEASURED_PEAKS.json, else the documented fallback."""
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        return float(json.loads(peaks_file.read_text()).get("hbm_gbs", 6650.0)), "MEASURED_PEAKS.json"
+    return 6650.0, "fallback"
+
+
+def _time_graph(fn, reps):
+    """Average milliseconds of fn() over one CUDA-graph replay of `reps` calls (CUDA events)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def run_sweep(args):
+    """BASELINE.json config 5: M in {16 .. 32768} x three layer shapes x (W4A8, W4A4+RHT), group-128 scales,
+    per-token activation scales; whole linear (pre-pass + GEMM), one input set per case (the working set of the
+    large cases exceeds L2 by itself, the small ones are latency-bound).  One JSON line with every case."""
+    import __graft_entry__ as entry
+    entry.load_package()
+    from fastwamjoint_quantization_b200 import native
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    int8_peak = measure_int8_peak(device)
+    hbm_peak, _ = measured_peaks()
+    gen = torch.Generator(device=device).manual_seed(0)
+    cases = []
+    for abits in (8, 4):
+        for (k, n) in ((3072, 3072), (3072, 12288), (12288, 3072)):
+            packed = torch.randint(0, 256, (n, k // 2), device=device, dtype=torch.uint8, generator=gen)
+            weight = native.prepack_weights(packed) if args.weights == "prepacked" else packed
+            scales = (torch.rand(n, k // 128, device=device, generator=gen) * 0.01 + 0.001).half()
+            signs = ((torch.randint(0, 2, (k,), device=device, generator=gen) * 2 - 1).float() if abits == 4 else None)
+            for m in (16, 64, 256, 1024, 4096, 16384, 32768):
+                x = torch.randn(m, k, device=device, generator=gen).bfloat16()
+                out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+                work = torch.empty(native._lib.load_library().sq_workspace_bytes(m, k), device=device, dtype=torch.uint8)
+                ms = _time_graph(lambda: native.linear(x, weight, scales, None, abits=abits, mode="token", signs=signs,
+                                                       out=out, workspace=work), 20 if m <= 4096 else 5)
+                ops = 2.0 * m * n * k
+                roof_ms = max(ops / (int8_peak * 1e12), algorithmic_bytes(m, k, n, abits == 4, args.weights) / (hbm_peak * 1e9)) * 1e3
+                cases.append({"abits": abits, "rht": abits == 4, "M": m, "K": k, "N": n, "us": round(ms * 1e3, 2),
+                              "tops": round(ops / ms / 1e9, 1), "frac": round(roof_ms / ms, 3)})
+                del x, out, work
+    status = native.device_status()
+    if status != 0:
+        raise SystemExit(f"device status {status}")
+    best = max(c["tops"] for c in cases)
+    print(json.dumps({"metric": "W4 linear int-TOPS, config-5 sweep (best case)", "value": best, "unit": "TOPS", "n_gpus": 1,
+                      "steps": 1, "warmup": 3, "ms_per_step": None, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "int8 x int4 -> int32", "data": "synthetic",
+                      "config": {"workload": "c5_sweep", "weights": args.weights, "weight_scales": "fp16 group-128",
+                                 "activation_scales": "per-token", "int8_peak_tops": round(int8_peak, 1),
+                                 "hbm_peak_gbs": hbm_peak},
+                      "sweep": cases}), flush=True)
+
+
+def run_channel(args):
+    """The reference's production scheme on one layer shape: static D / gain / clip schedule, per-channel fp32
+    weight scales, int4 activations (runtime.py:138-175; kernels w4a4.cu).  GEMM kernel alone and whole linear."""
+    import __graft_entry__ as entry
+    entry.load_package()
+    from fastwamjoint_quantization_b200 import native
+    oracle = load_oracle()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    m, k, n = 4096, 3072, 12288
+    gen = torch.Generator().manual_seed(0)
+    x = (torch.randn(1, m, k, generator=gen) * 0.5).bfloat16()
+    qw = torch.randint(-7, 8, (n, k), generator=gen, dtype=torch.int8)
+    ws = torch.full((n,), 1 / 512)
+    inverse = torch.pow(2.0, torch.randint(-1, 2, (k,), generator=gen).float())
+    counts = (m // 2, m // 2)
+    gains = torch.tensor([[0.5, 2.0], [2.0, 0.5]])
+    act = torch.tensor([0.125, 0.25])
+    packed = oracle.pack_signed_int4(qw).to(device)
+    weight = native.prepack_weights(packed) if args.weights == "prepacked" else packed
+    xd, wsd, invd, actd, gaind = (t.to(device) for t in (x, ws, inverse, act, gains))
+    out = torch.empty(1, m, n, device=device, dtype=torch.bfloat16)
+    work = torch.empty(native._lib.load_library().sq_workspace_bytes(m, k), device=device, dtype=torch.uint8)
+    step = lambda: native.linear(xd, weight, wsd, None, abits=4, mode="static", inverse=invd, act_scales=actd,
+                                 gains=gaind, call=1, span=counts[0], streams=2, out=out, workspace=work)
+    got = step()
+    rows = 64
+    want = oracle.linear_static(x[:, :rows], qw, ws, None, inverse, act, gains, (rows, 0), 1, abits=4)["out"]
+    if not torch.equal(got[:, :rows].cpu(), want):
+        raise SystemExit("per-channel static linear differs from the kernel-order oracle (expected bit equality)")
+    codes, row_scales = native.prepass(xd, abits=4, mode="static", inverse=invd, act_scale=actd[1:], gains=gaind[1],
+                                       span=counts[0], streams=2)
+    gemm = lambda: native.gemm(codes, weight, wsd, row_scales, None, out_dtype=torch.bfloat16, out=out.view(m, n),
+                               int4_range=True)
+    int8_peak = measure_int8_peak(device)
+    sampler = ClockSampler(0)
+    sampler.start()
+    step_ms = _time_graph(step, args.steps)
+    gemm_ms = _time_graph(gemm, args.steps)
+    clocks = sampler.stop()
+    ops = 2.0 * m * n * k
+    print(json.dumps({"metric": "W4A4 per-channel static linear int-TOPS", "value": ops / step_ms / 1e9, "unit": "TOPS",
+                      "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": step_ms, "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32", "data": "synthetic",
+                      "config": {"workload": "m4096_ffn_up_channel", "M": m, "K": k, "N": n, "abits": 4,
+                                 "weight_scales": "fp32 per channel", "activation_scales": "static schedule, two streams",
+                                 "weights": args.weights, "l2": "inputs of one step (65 MB) + outputs (100 MB) > 126 MB L2",
+                                 "launch": "the K steps are replayed as one CUDA graph"},
+                      "gpu_launches": 2 * args.steps,
+                      "roofline": {"bound": "tensor", "achieved": ops / gemm_ms / 1e9, "peak": int8_peak, "unit": "TOP/s",
+                                   "frac": ops / gemm_ms / 1e9 / int8_peak, "traffic": None, "kernel": "sq_gemm_tc_kernel",
+                                   "gemm_ms": gemm_ms},
+                      "clocks": clocks, "parity": "bit-equal to the kernel-order oracle on the checked rows"}), flush=True)
+
+
 def run_nsplit(args):
     """Output-channel split of the widest layer (3072 -> 12288, W4A4+RHT, M = 4096 tokens on every rank): rank r
     holds W[r*N/G:(r+1)*N/G], computes [M, N/G] and the slices are all-gathered with NCCL over NVLink.  The
@@ -367,7 +492,8 @@ def main():
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
-    parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(DIT_WORKLOADS) + ["nsplit_ffn_up"])
+    parser.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(DIT_WORKLOADS) +
+                        ["nsplit_ffn_up", "c5_sweep", "m4096_ffn_up_channel"])
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--weights", default="prepacked", choices=["prepacked", "packed"],
@@ -378,6 +504,13 @@ def main():
         if args.steps == 200:
             args.steps = 50
         run_nsplit(args)
+        return
+    if args.workload in ("c5_sweep", "m4096_ffn_up_channel"):
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the B200 path has no CPU fallback.")
+        if args.steps == 200:
+            args.steps = 20
+        (run_sweep if args.workload == "c5_sweep" else run_channel)(args)
         return
     if args.workload in DIT_WORKLOADS:
         if args.steps == 200:
