@@ -327,6 +327,7 @@ int sq_linear_scheduled(const void* x, int x_dtype, int64_t rows, int64_t K, int
                                   streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
                                   static_cast<cudaStream_t>(stream), &fusion);
   if (status != SQ_OK) return status;
+  a.after_prepass = true;
   return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
 }
 
@@ -386,6 +387,7 @@ int sq_linear_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int
                                         streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
                                         static_cast<cudaStream_t>(stream), &rotation);
   if (status != SQ_OK) return status;
+  a.after_prepass = true;
   return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -229,6 +229,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Launched as a programmatic dependent of the pre-pass (sq_linear*), this kernel may become resident while the
+  // pre-pass still runs: everything above touches only this CTA's shared and tensor memory.  From here on the
+  // codes and row scales are read, so wait for the pre-pass grid (a no-op for an ordinary launch).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int num_tiles = p.ch_tiles * p.tok_tiles;
   const bool tracing = kTrace && blockIdx.x == 0 && p.timeline != nullptr;
@@ -707,8 +711,23 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
     const int regs = (dev >= 0 && dev < 64) ? launch_regs[dev] : 0;
     if (regs * kThreads < kRegisterPoolNeeded) return SQ_ERR_DRIVER;
   }
-  kernel<<<grid, kThreads, smem, stream>>>(tmap_codes, tmap_packed, p);
-  cudaError_t err = cudaGetLastError();
+  cudaError_t err;
+  if (a.after_prepass) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(grid));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    err = cudaLaunchKernelEx(&config, kernel, tmap_codes, tmap_packed, p);
+  } else {
+    kernel<<<grid, kThreads, smem, stream>>>(tmap_codes, tmap_packed, p);
+    err = cudaGetLastError();
+  }
   return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
 }
 

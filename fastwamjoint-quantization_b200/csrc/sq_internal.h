@@ -47,6 +47,7 @@ struct GemmArgs {
   int out_dtype;
   int64_t M, N, K;
   int32_t* acc_dump;
+  bool after_prepass = false;  // launched right behind the pre-pass that writes codes / row_scales: overlap the prologue
   bool weights_prepacked = false;  // SQ_WEIGHTS_PREPACKED: w_packed is int8 [N, K] from sq_prepack_weights
   bool codes_int4_range = false;  // SQ_CODES_INT4_RANGE was set: every code lies in [-8, 7]
   // fused epilogue: out = residual + gate * act(acc * scales + bias)

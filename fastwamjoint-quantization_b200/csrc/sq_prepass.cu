@@ -160,6 +160,8 @@ __device__ __forceinline__ uint32_t round_code(float q, float qmax) {
 // dynamic shared memory: one fp32 row per row of the CTA, then the matrix).
 template <typename T, int VPT, bool kFused, bool kMix = false>
 __global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepass_kernel(const PrepassParams p) {
+  // lets a GEMM launched as this grid's programmatic dependent set itself up while this grid still runs
+  asm volatile("griddepcontrol.launch_dependents;");
   const int tpr = 1 << p.tpr_log2;
   const int t = threadIdx.x & (tpr - 1);
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> p.tpr_log2) + (threadIdx.x >> p.tpr_log2);
