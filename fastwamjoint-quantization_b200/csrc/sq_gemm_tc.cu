@@ -849,9 +849,9 @@ int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t st
 }
 
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M == 0) return SQ_OK;  // nothing to do; an empty tensor may come with a null pointer
   int v = validate_gemm(a);
   if (v != SQ_OK) return v;
-  if (a.M == 0) return SQ_OK;
   if (a.wscale_mode == SQ_WSCALE_GROUP_F16) return launch_mode<true>(a, stream);
   return launch_mode<false>(a, stream);
 }

@@ -521,6 +521,7 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
                    const float* signs, int rht_block, const float* act_scale, const float* gains, int64_t span,
                    int64_t streams, int64_t seq_tokens, int codes_layout, int pack_int4, void* codes,
                    float* row_scales, cudaStream_t stream, const PrepassFusion* fusion) {
+  if (rows == 0) return SQ_OK;  // nothing to do; an empty tensor may come with a null pointer
   if (x == nullptr || codes == nullptr || row_scales == nullptr) return SQ_ERR_NULL;
   PrepassFusion none;
   const PrepassFusion& f = fusion != nullptr ? *fusion : none;

@@ -301,6 +301,31 @@ def test_linear_graph_capture_and_replay_after_mutation(native, oracle):
     assert torch.equal(captured, run())
 
 
+def test_empty_and_ragged_token_counts(native, oracle):
+    """Edges of the token axis: no rows at all (nothing is launched, an empty result comes back), one row, and
+    counts that leave a partial 16-row MMA column block and a partial tile (129 = 128 + 1, 145 = 128 + 16 + 1),
+    on both weight forms; rows past M must not be written."""
+    k, n = 512, 264  # N = 2 full channel tiles + 8 channels
+    case = oracle.prepare_token_linear(160, k, n, abits=8, seed=4)
+    packed = oracle.pack_signed_int4(case["qweight"]).cuda()
+    tiled = native.prepack_weights(packed)
+    scales, bias = case["weight_scales"].cuda(), case["bias"].cuda()
+    empty = native.linear(case["x"][:0].cuda(), packed, scales, bias, abits=8, mode="token")
+    assert empty.shape == (0, n) and native.device_status() == 0
+    codes, rows = native.prepass(case["x"][:0].cuda(), abits=8, mode="token")
+    assert codes.shape == (0, k) and rows.shape == (0,)
+    for m in (1, 15, 17, 129, 145, 160):
+        x = case["x"][:m]
+        want = oracle.linear_token(x, case["qweight"], case["weight_scales"], case["bias"], abits=8,
+                                   signs=None, want_accumulators=False)["out"]
+        for weight in (packed, tiled):
+            guard = torch.full((m + 3, n), 7.0, device="cuda", dtype=torch.bfloat16)
+            out = native.linear(x.cuda(), weight, scales, bias, abits=8, mode="token", out=guard[:m])
+            assert rel_fro(out.cpu(), want) < 2e-3
+            assert torch.all(guard[m:] == 7.0)  # nothing written past the last row
+    assert native.device_status() == 0
+
+
 def test_mma_rate_probe(native):
     """The tensor-pipe probe runs, finishes (bounded wait, status 0) and reports a plausible time per MMA:
     at least the 32 cycles a K = 32 step of 128 x 64 would take at twice the nominal rate, at most 1000."""
