@@ -546,17 +546,26 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         OutT* out = static_cast<OutT*>(p.out) + n;
         const float* rs_ptr = p.row_scales + tok0 + my_col0;
         const int64_t m0 = tok0 + my_col0;
+        // row scales of four columns at a time, requested one step ahead of their use
+        auto row_scales4 = [&](int j) {
+          float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (4 * j + 4 <= my_cols) {
+            v = __ldg(reinterpret_cast<const float4*>(rs_ptr) + j);
+          } else if (4 * j < my_cols) {
+            v.x = __ldg(rs_ptr + 4 * j);
+            if (4 * j + 1 < my_cols) v.y = __ldg(rs_ptr + 4 * j + 1);
+            if (4 * j + 2 < my_cols) v.z = __ldg(rs_ptr + 4 * j + 2);
+          }
+          return v;
+        };
+        // (group form only: in the channel form the extra live registers cost more than the latency saved)
+        float4 ahead = kGroup ? row_scales4(0) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
         for (int j = 0; j < kCols / 4; ++j) {
+          const float4 current = kGroup ? ahead : row_scales4(j);
+          if (kGroup && j + 1 < kCols / 4) ahead = row_scales4(j + 1);
           if (4 * j < my_cols) {
-            float rs[4];
-            if (4 * j + 4 <= my_cols) {
-              const float4 v = __ldg(reinterpret_cast<const float4*>(rs_ptr) + j);
-              rs[0] = v.x; rs[1] = v.y; rs[2] = v.z; rs[3] = v.w;
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) rs[e] = (4 * j + e < my_cols) ? __ldg(rs_ptr + 4 * j + e) : 0.0f;
-            }
+            const float rs[4] = {current.x, current.y, current.z, current.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               if (4 * j + e < my_cols) {
