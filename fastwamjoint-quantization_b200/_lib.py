@@ -30,6 +30,9 @@ _SIGNATURES = {
                            c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "sq_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                         c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "sq_gemm_split": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                              c_int64, c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "sq_split_workspace_bytes": (c_size_t, [c_int64]),
     "sq_gemm_check": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                               c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "sq_gemm_timeline": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
@@ -61,6 +64,7 @@ _SIGNATURES = {
     "sq_linear_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                   c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "sq_wait_probe": (c_int, [c_int64, c_void_p, c_void_p]),
     "sq_device_status": (c_int, []),
     "sq_status_string": (c_char_p, [c_int]),
     "sq_version": (c_char_p, []),

@@ -19,7 +19,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "lib" / "libsq_b200.so"
-SOURCES = ("sq_prepass.cu", "sq_gemm_tc.cu", "sq_api.cu")
+SOURCES = ("sq_prepass.cu", "sq_gemm_tc.cu", "sq_gemm_ts.cu", "sq_api.cu")
 HEADERS = ("sq_internal.h", "sq_ptx.cuh", "../../include/sq_b200.h")
 NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden")

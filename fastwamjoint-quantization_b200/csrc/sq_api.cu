@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 #include "sq_internal.h"
@@ -17,8 +19,7 @@ __device__ int g_device_status = 0;
 int* device_status_word() {
   static int* cached[64] = {nullptr};
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;  // callers treat null as a driver error
   if (cached[dev] == nullptr) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_device_status) == cudaSuccess) cached[dev] = static_cast<int*>(ptr);
@@ -42,9 +43,35 @@ int validate_gemm(const GemmArgs& a) {
   if (a.wscale_mode == SQ_WSCALE_GROUP_F16 && a.K % 128 != 0) return SQ_ERR_SHAPE;
   if (a.M > (int64_t{1} << 30) || a.N > (int64_t{1} << 30) || a.K > 131072) return SQ_ERR_SHAPE;
   if (!aligned16(a.codes) || !aligned16(a.w_packed) || !aligned16(a.out)) return SQ_ERR_SHAPE;
-  // unpacked weights are stored in the even-odd k order and carry no path for the accumulator dump
-  if (a.weights_prepacked && (a.codes_layout != SQ_CODES_EVEN_ODD || a.acc_dump != nullptr)) return SQ_ERR_ENUM;
+  // the drain reads row scales four at a time; scales, bias, gate, residual and the dump are read or written
+  // element by element in their own types
+  if (!aligned16(a.row_scales)) return SQ_ERR_SHAPE;
+  const uintptr_t scale_align = a.wscale_mode == SQ_WSCALE_GROUP_F16 ? 2u : 4u;
+  if ((reinterpret_cast<uintptr_t>(a.w_scales) & (scale_align - 1)) != 0) return SQ_ERR_SHAPE;
+  if (((reinterpret_cast<uintptr_t>(a.bias) | reinterpret_cast<uintptr_t>(a.gate) |
+        reinterpret_cast<uintptr_t>(a.residual)) & 1u) != 0)
+    return SQ_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(a.acc_dump) & 3u) != 0) return SQ_ERR_SHAPE;
+  // unpacked weights are stored in the even-odd k order
+  if (a.weights_prepacked && a.codes_layout != SQ_CODES_EVEN_ODD) return SQ_ERR_ENUM;
   return SQ_OK;
+}
+
+// ------------------------------------------------------------------ kernel choice
+// SQ_GEMM_KERNEL=tc in the environment (read once) keeps the first-generation kernel for comparisons.
+static bool first_generation_requested() {
+  static const bool requested = [] {
+    const char* value = std::getenv("SQ_GEMM_KERNEL");
+    return value != nullptr && std::strcmp(value, "tc") == 0;
+  }();
+  return requested;
+}
+
+bool gemm_takes_split_workspace(const GemmArgs& a) { return !a.weights_prepacked && !first_generation_requested(); }
+
+int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
+  if (a.weights_prepacked || first_generation_requested()) return launch_gemm_tc(a, stream);
+  return launch_gemm_ts(a, stream);
 }
 
 // ------------------------------------------------------------------ weight prepack
@@ -149,6 +176,20 @@ int launch_gemm_check(const GemmArgs& a, cudaStream_t stream) {
 
 static size_t round256(size_t v) { return (v + 255u) & ~static_cast<size_t>(255u); }
 
+// sq_linear*: a workspace that is larger than codes + row scales by sq_split_workspace_bytes() lends the GEMM its
+// tail for tiles split along K; the pre-pass in front clears the counters at the head of that area.
+static void attach_split_area(GemmArgs& a, void* workspace, size_t workspace_bytes, int64_t rows, int64_t K,
+                              PrepassFusion* prepass) {
+  if (rows <= 0 || !gemm_takes_split_workspace(a)) return;
+  const size_t basic = round256(static_cast<size_t>(rows) * static_cast<size_t>(K)) + round256(static_cast<size_t>(rows) * 4u);
+  const size_t extra = gemm_split_workspace_bytes(rows);
+  if (workspace_bytes < basic + extra) return;
+  a.split_workspace = static_cast<uint8_t*>(workspace) + basic;
+  a.split_workspace_bytes = extra;
+  a.split_counters_cleared = true;
+  prepass->clear_words = static_cast<int*>(a.split_workspace);
+}
+
 // ------------------------------------------------------------------ library-owned scratch (sq_linear_noalloc)
 // Scratch for callers that cannot allocate: a fixed array in the library's own device image.  Every GPU that
 // loads the library carries it until the process exits.  In host code the name below is only a handle for
@@ -213,10 +254,25 @@ static sq::GemmArgs make_args(const void* codes, int codes_layout, const void* w
 int sq_gemm(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
             const float* row_scales, const void* bias, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
             int32_t* acc_dump, void* stream) {
-  return sq::launch_gemm_tc(make_args(codes, codes_layout, w_packed, w_scales, wscale_mode, row_scales, bias, out,
-                                      out_dtype, M, N, K, acc_dump),
-                            static_cast<cudaStream_t>(stream));
+  return sq::launch_gemm(make_args(codes, codes_layout, w_packed, w_scales, wscale_mode, row_scales, bias, out,
+                                   out_dtype, M, N, K, acc_dump),
+                         static_cast<cudaStream_t>(stream));
 }
+
+int sq_gemm_split(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+                  const float* row_scales, const void* bias, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                  int32_t* acc_dump, void* split_workspace, size_t split_workspace_bytes, void* stream) {
+  sq::GemmArgs a = make_args(codes, codes_layout, w_packed, w_scales, wscale_mode, row_scales, bias, out, out_dtype, M,
+                             N, K, acc_dump);
+  if (split_workspace != nullptr && (reinterpret_cast<uintptr_t>(split_workspace) & 15u) != 0) return SQ_ERR_SHAPE;
+  if (sq::gemm_takes_split_workspace(a)) {
+    a.split_workspace = split_workspace;
+    a.split_workspace_bytes = split_workspace_bytes;
+  }
+  return sq::launch_gemm(a, static_cast<cudaStream_t>(stream));
+}
+
+size_t sq_split_workspace_bytes(int64_t M) { return sq::gemm_split_workspace_bytes(M); }
 
 int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
                   const float* row_scales, const void* bias, void* out, int out_dtype, int64_t M, int64_t N,
@@ -228,9 +284,10 @@ int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, con
 
 int sq_gemm_timeline(const void* codes, const void* w_packed, const void* w_scales, const float* row_scales,
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K, long long* timeline, void* stream) {
-  return sq::launch_gemm_timeline(make_args(codes, SQ_CODES_EVEN_ODD, w_packed, w_scales, SQ_WSCALE_GROUP_F16, row_scales,
-                                            bias, out, SQ_BF16, M, N, K, nullptr),
-                                  timeline, static_cast<cudaStream_t>(stream));
+  const sq::GemmArgs a = make_args(codes, SQ_CODES_EVEN_ODD | SQ_CODES_INT4_RANGE, w_packed, w_scales,
+                                   SQ_WSCALE_GROUP_F16, row_scales, bias, out, SQ_BF16, M, N, K, nullptr);
+  if (sq::first_generation_requested()) return sq::launch_gemm_timeline(a, timeline, static_cast<cudaStream_t>(stream));
+  return sq::launch_gemm_ts_timeline(a, timeline, static_cast<cudaStream_t>(stream));
 }
 
 int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled, void* stream) {
@@ -240,6 +297,10 @@ int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled
 
 int sq_mma_rate(int n_cols, int iterations, long long* cycles, void* stream) {
   return sq::launch_mma_rate(n_cols, iterations, cycles, static_cast<cudaStream_t>(stream));
+}
+
+int sq_wait_probe(int64_t limit_us, long long* waited_ns, void* stream) {
+  return sq::launch_wait_probe(limit_us, waited_ns, static_cast<cudaStream_t>(stream));
 }
 
 size_t sq_workspace_bytes(int64_t M, int64_t K) {
@@ -323,12 +384,13 @@ int sq_linear_scheduled(const void* x, int x_dtype, int64_t rows, int64_t K, int
     int v = sq::validate_gemm(a);
     if (v != SQ_OK) return v;
   }
+  sq::attach_split_area(a, workspace, workspace_bytes, rows, K, &fusion);
   int status = sq::launch_prepass(x, x_dtype, rows, K, abits, mode, inv_d, signs, rht_block, act_scale, gain_row, span,
                                   streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
                                   static_cast<cudaStream_t>(stream), &fusion);
   if (status != SQ_OK) return status;
   a.after_prepass = true;
-  return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
+  return sq::launch_gemm(a, static_cast<cudaStream_t>(stream));
 }
 
 int sq_prepass_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int abits, int mode, const float* inv_d,
@@ -383,12 +445,13 @@ int sq_linear_composite(const void* x, int x_dtype, int64_t rows, int64_t K, int
     rotation.call_index = call_index;
     rotation.calls = calls;
   }
+  sq::attach_split_area(a, workspace, workspace_bytes, rows, K, &rotation);
   const int status = sq::launch_prepass(x, x_dtype, rows, K, abits, mode, inv_d, signs, 0, act_scale, gain_row, span,
                                         streams, seq_tokens, SQ_CODES_EVEN_ODD, 0, codes, row_scales,
                                         static_cast<cudaStream_t>(stream), &rotation);
   if (status != SQ_OK) return status;
   a.after_prepass = true;
-  return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
+  return sq::launch_gemm(a, static_cast<cudaStream_t>(stream));
 }
 
 int sq_linear_noalloc(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
@@ -432,6 +495,15 @@ const char* sq_status_string(int status) {
     case SQ_ERR_DEVICE_WAIT: return "a kernel gave up a bounded wait";
     case SQ_ERR_SCRATCH_LIMIT: return "rows * K is beyond the library-owned scratch of sq_linear_noalloc";
     case 9006: return "device: the MMA rate probe timed out waiting for its MMAs";
+    case 9101: return "device: TMA producer timed out waiting for a free stage";
+    case 9102: return "device: MMA warp timed out waiting for a free accumulator";
+    case 9103: return "device: MMA warp timed out waiting for operands";
+    case 9104: return "device: unpack warp timed out waiting for packed weights or a free weight stage";
+    case 9105: return "device: drain warp timed out waiting for an accumulator";
+    case 9107: return "device: TMA producer timed out waiting for a free row-scale slot";
+    case 9108: return "device: drain warps timed out meeting around a split tile";
+    case 9109: return "device: drain warp timed out waiting for row scales";
+    case 9190: return "device: the wait probe gave up, as it is meant to";
     case 9001: return "device: TMA producer timed out waiting for a free stage";
     case 9002: return "device: MMA warp timed out waiting for a free accumulator";
     case 9003: return "device: MMA warp timed out waiting for operands";

@@ -688,6 +688,7 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   TcParams p;
   p.w_scales = a.w_scales; p.row_scales = a.row_scales; p.bias = a.bias; p.out = a.out;
   p.acc_dump = a.acc_dump; p.timeline = timeline; p.status = device_status_word();
+  if (p.status == nullptr) return SQ_ERR_DRIVER;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
   p.tok_tile = tok_tile;
@@ -769,7 +770,7 @@ int launch_mode(const GemmArgs& a, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------- tensor-pipe rate probe
 // One warp per SM issues `iters` x 4 kind::i8 MMAs (M = 128, N = kN, K = 32) back to back on fixed shared-memory
 // tiles, commits once and waits (bounded); thread block 0 reports the SM cycles from first issue to completion.
-template <int kN>
+template <int kN, bool kTs = false>
 __global__ void __launch_bounds__(128, 1) sq_mma_rate_kernel(long long* cycles, int iters, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -805,7 +806,11 @@ __global__ void __launch_bounds__(128, 1) sq_mma_rate_kernel(long long* cycles, 
       for (int it = 0; it < iters; ++it) {
         const uint32_t d = tmem + (it & 1) * 256;
 #pragma unroll
-        for (int k = 0; k < kBlockK / kUmmaK; ++k) umma_i8(d, desc_a + 2 * k, desc_b + 2 * k, idesc, k > 0 ? 1u : 0u);
+        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+          // kTs: operand A from tensor memory (whatever columns 384.. hold; only the rate matters)
+          if (kTs) umma_i8_ts(d, tmem + 384 + 8 * k, desc_b + 2 * k, idesc, k > 0 ? 1u : 0u);
+          else umma_i8(d, desc_a + 2 * k, desc_b + 2 * k, idesc, k > 0 ? 1u : 0u);
+        }
       }
       umma_commit(bar);
     }
@@ -822,12 +827,14 @@ __global__ void __launch_bounds__(128, 1) sq_mma_rate_kernel(long long* cycles, 
   }
 }
 
-template <int kN>
+template <int kN, bool kTs = false>
 int launch_mma_rate_n(long long* cycles, int iters, cudaStream_t stream) {
   const int smem = static_cast<int>(kWBytes) + kN * kBlockK + 2048;
-  cudaError_t err = cudaFuncSetAttribute(sq_mma_rate_kernel<kN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t err = cudaFuncSetAttribute(sq_mma_rate_kernel<kN, kTs>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) return static_cast<int>(err);
-  sq_mma_rate_kernel<kN><<<sm_count(), 128, smem, stream>>>(cycles, iters, device_status_word());
+  int* status = device_status_word();
+  if (status == nullptr) return SQ_ERR_DRIVER;
+  sq_mma_rate_kernel<kN, kTs><<<sm_count(), 128, smem, stream>>>(cycles, iters, status);
   err = cudaGetLastError();
   return err == cudaSuccess ? SQ_OK : static_cast<int>(err);
 }
@@ -841,6 +848,7 @@ int launch_mma_rate(int n_cols, int iters, long long* cycles, cudaStream_t strea
     case 64: return launch_mma_rate_n<64>(cycles, iters, stream);
     case 128: return launch_mma_rate_n<128>(cycles, iters, stream);
     case 256: return launch_mma_rate_n<256>(cycles, iters, stream);
+    case 0x1000 + 128: return launch_mma_rate_n<128, true>(cycles, iters, stream);  // weights from tensor memory
     default: return SQ_ERR_ENUM;
   }
 }
@@ -861,6 +869,7 @@ int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   if (a.M == 0) return SQ_OK;  // nothing to do; an empty tensor may come with a null pointer
   int v = validate_gemm(a);
   if (v != SQ_OK) return v;
+  if (a.weights_prepacked && a.acc_dump != nullptr) return SQ_ERR_ENUM;  // the prepacked variants carry no dump path
   if (a.wscale_mode == SQ_WSCALE_GROUP_F16) return launch_mode<true>(a, stream);
   return launch_mode<false>(a, stream);
 }

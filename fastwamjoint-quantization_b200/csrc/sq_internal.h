@@ -25,6 +25,8 @@ struct PrepassFusion {
   // then the bases of the [calls] and [calls, streams] tables
   const int32_t* call_index = nullptr;
   int64_t calls = 0;
+  // 256 ints (1024 bytes) thread block 0 clears before anything else: the K-split counters of the GEMM behind it
+  int* clear_words = nullptr;
   // composite rotation: K = mix_order x (power of two); replaces the block rotation, excludes the fusions above
   const float* mix = nullptr;        // [mix_order, mix_order] of +-1
   int mix_order = 0;
@@ -56,17 +58,31 @@ struct GemmArgs {
   int64_t gate_span = 1;
   int64_t gate_row_stride = 0;     // elements between gate rows
   const void* residual = nullptr;  // [M, N] in out's dtype
+  // scratch for tiles that are split along K (see sq_gemm_ts.cu); null: whole tiles only
+  void* split_workspace = nullptr;
+  size_t split_workspace_bytes = 0;
+  bool split_counters_cleared = false;  // the caller already put a memset of the first 1024 bytes on the stream
 };
 
 int validate_gemm(const GemmArgs& a);
 int launch_prepack_weights(const uint8_t* w_packed, int64_t N, int64_t K, int8_t* w_tiled, cudaStream_t stream);
 int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
+// Second-generation kernel (weights in tensor memory, K-split scheduling); packed int4 weights only.
+int launch_gemm_ts(const GemmArgs& a, cudaStream_t stream);
+int launch_gemm_ts_timeline(const GemmArgs& a, long long* timeline, cudaStream_t stream);
+size_t gemm_split_workspace_bytes(int64_t M);
+// Picks the kernel: the second-generation one unless the weights are prepacked or SQ_GEMM_KERNEL=tc is set.
+int launch_gemm(const GemmArgs& a, cudaStream_t stream);
+bool gemm_takes_split_workspace(const GemmArgs& a);
 int launch_gemm_check(const GemmArgs& a, cudaStream_t stream);
 // Group-scale bf16 GEMM with M > 128 only: same result, plus clock stamps of CTA 0's pipeline roles.
 int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t stream);
 
 // Tensor-pipe rate probe: n_cols in {64, 128, 256}; cycles is a device int64.
 int launch_mma_rate(int n_cols, int iters, long long* cycles, cudaStream_t stream);
+
+// One CTA waits `limit_us` for a barrier nobody arrives at, then reports status 9190 (see sq_wait_probe).
+int launch_wait_probe(int64_t limit_us, long long* waited_ns, cudaStream_t stream);
 
 // Device-side status word (0 = fine).  Written by kernels that gave up a bounded wait.
 int* device_status_word();

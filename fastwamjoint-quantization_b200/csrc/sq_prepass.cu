@@ -97,6 +97,7 @@ struct PrepassParams {
   // static mode with the schedule entry chosen on the device: act_scale / gains are then the table bases
   const int32_t* call_index;
   int64_t calls;
+  int* clear_words;      // 256 ints thread block 0 sets to zero (the GEMM's K-split counters), or null
   // composite rotation (kMix): K = mix_order x part, part a power of two in [8, 512]
   const float* mix;      // [mix_order, mix_order] entries +-1, row-major
   int mix_order;
@@ -162,6 +163,7 @@ template <typename T, int VPT, bool kFused, bool kMix = false>
 __global__ void __maxnreg__((VPT <= 3 && !kFused && !kMix) ? 48 : 128) sq_prepass_kernel(const PrepassParams p) {
   // lets a GEMM launched as this grid's programmatic dependent set itself up while this grid still runs
   asm volatile("griddepcontrol.launch_dependents;");
+  if (p.clear_words != nullptr && blockIdx.x == 0 && threadIdx.x < 256) p.clear_words[threadIdx.x] = 0;
   const int tpr = 1 << p.tpr_log2;
   const int t = threadIdx.x & (tpr - 1);
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> p.tpr_log2) + (threadIdx.x >> p.tpr_log2);
@@ -537,6 +539,15 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
   if (pack_int4 != 0 && (pack_int4 != 1 || abits != 4 || codes_layout != SQ_CODES_NATURAL)) return SQ_ERR_ENUM;
   if (rows < 0 || K <= 0 || (K & 7) != 0 || K > 32768) return SQ_ERR_SHAPE;
   if (rows == 0) return SQ_OK;
+  {
+    // everything the kernel reads or writes as 8- or 16-byte vectors; a misaligned pointer is refused here, on
+    // the host, instead of becoming a misaligned-address fault on the device
+    auto aligned = [](const void* ptr, uintptr_t bytes) { return (reinterpret_cast<uintptr_t>(ptr) & (bytes - 1)) == 0; };
+    if (!aligned(x, 16) || !aligned(codes, 16) || !aligned(row_scales, 4)) return SQ_ERR_SHAPE;
+    if (!aligned(signs, 16) || !aligned(inv_d, 16)) return SQ_ERR_SHAPE;
+    if (!aligned(f.norm_weight, 16) || !aligned(f.mod_scale, 16) || !aligned(f.mod_shift, 16)) return SQ_ERR_SHAPE;
+    if (!aligned(f.mix, 4) || !aligned(act_scale, 4) || !aligned(gains, 4) || !aligned(f.call_index, 4)) return SQ_ERR_SHAPE;
+  }
   if (rows > (int64_t{1} << 31) - 1) return SQ_ERR_SHAPE;
   int lanes_log2 = 0;
   float norm = 1.0f;
@@ -583,6 +594,7 @@ int launch_prepass(const void* x, int x_dtype, int64_t rows, int64_t K, int abit
   p.mod_scale = f.mod_scale; p.mod_shift = f.mod_shift;
   p.mod_span = f.mod_span > 0 ? f.mod_span : 1; p.mod_row_stride = f.mod_row_stride; p.round_after = f.round_after;
   p.call_index = f.call_index; p.calls = f.calls;
+  p.clear_words = f.clear_words;
   p.mix = f.mix; p.mix_order = f.mix_order; p.mix_part_log2 = part_log2;
   p.mix_part_norm = static_cast<float>(1.0 / std::sqrt(static_cast<double>(int64_t{1} << part_log2)));
   p.mix_order_root = static_cast<float>(std::sqrt(static_cast<double>(f.mix_order > 0 ? f.mix_order : 1)));

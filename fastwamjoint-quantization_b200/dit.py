@@ -165,7 +165,8 @@ class SyntheticDiT(nn.Module):
         self.blocks = nn.ModuleList(DiTBlock(config, i, device, dtype, backend) for i in range(config.blocks))
         if backend == "native":
             biggest = max(config.hidden, config.ffn)
-            size = native._lib.load_library().sq_workspace_bytes(config.tokens, biggest)
+            lib = native._lib.load_library()
+            size = lib.sq_workspace_bytes(config.tokens, biggest) + lib.sq_split_workspace_bytes(config.tokens)
             self.register_buffer("workspace", torch.empty(size, dtype=torch.uint8, device=device), persistent=False)
             for module in self.modules():
                 if isinstance(module, TokenQuantLinear):

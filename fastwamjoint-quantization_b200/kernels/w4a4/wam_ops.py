@@ -9,6 +9,7 @@ import torch
 
 from .._common import (GROUP, adaln_linear, check_common, dynamic_linear, gate_residual_linear, scheduled_linear,
                        stream_span)
+from ...rht import official_rotation_matrix, official_rotation_plan
 from .loader import load_extension  # noqa: F401
 
 
@@ -30,13 +31,22 @@ def symmetric_scheduled_stream_linear(x, packed, scales, bias, inverse, activati
 
 
 def symmetric_scheduled_stream_rht_linear(x, packed, scales, bias, inverse, activation_scales, gains, token_counts,
-                                          call, signs, *, rht_block: int = GROUP, mix=None):
-    """Rotate, scale, quantize to int4, multiply (``wam_ops.py:56-75``).  The rotation is the block-local
-    power-of-two Hadamard transform of length ``rht_block``, or - with ``mix``, an fp32 ``[order, order]`` sign
-    matrix - the reference's composite rotation ``order x power of two`` (had12 x H256 at K = 3072, had28 x H512
-    at K = 14336, ``rht.py:27-39``)."""
+                                          call, signs, *, rht_block: int | None = None, mix=None):
+    """Rotate, scale, quantize to int4, multiply (``wam_ops.py:56-75``).  Called as the reference calls it - no
+    keyword - the rotation is the reference's for the width (``rht.py:27-39``; device producer
+    ``rht.cuh:78-100``): the full-width transform for powers of two, had12 x H256 at K = 3072, had28 x H512 at
+    K = 14336, a ``ValueError`` for anything else.  ``rht_block`` opts into a block-local power-of-two transform
+    of that length instead, ``mix`` (fp32 ``[order, order]`` sign matrix) into a caller's own composite
+    ``order x power of two``.  The first call per width and device caches a small matrix on the device: make it
+    outside CUDA-graph capture (the warm-up runs of ``LiveJointDiTGraph`` do)."""
     x = _common(x, packed, scales, bias, inverse)
     span = stream_span(x, gains, token_counts, activation_scales, strict_positive=True)
+    if mix is None and rht_block is None:
+        kind, what = official_rotation_plan(x.shape[-1])
+        if kind == "block":
+            rht_block = int(what)
+        else:
+            mix = official_rotation_matrix(x.shape[-1], x.device)
     if mix is not None:
         return scheduled_linear(x, packed, scales, bias, inverse, activation_scales, gains, span, call, abits=4,
                                 signs=_check_signs(x, signs), mix=mix)

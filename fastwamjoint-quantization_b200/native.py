@@ -90,11 +90,14 @@ def _mix_matrix(mix: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
 
 def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_scales: torch.Tensor, bias,
          *, out_dtype: torch.dtype, codes_layout: int = _lib.CODES_EVEN_ODD, want_accumulators: bool = False,
-         check_kernel: bool = False, out: torch.Tensor | None = None, int4_range: bool = False):
+         check_kernel: bool = False, out: torch.Tensor | None = None, int4_range: bool = False,
+         split: bool = True):
     """codes int8 [M, K] x packed uint8 [N, K/2] -> [M, N] in ``out_dtype``.
     ``w_scales`` fp32 [N] selects the per-channel form, fp16 [N, K/128] the group form.
     ``int4_range`` promises that every code lies in [-8, 7] (SQ_CODES_INT4_RANGE): faster group form.
-    ``check_kernel`` runs the CUDA-core cross-check kernel instead of the tensor-core one (tests only)."""
+    ``check_kernel`` runs the CUDA-core cross-check kernel instead of the tensor-core one (tests only).
+    ``split`` lends the kernel scratch for tiles split along K (``sq_gemm_split``); without it only whole
+    tiles are scheduled."""
     _require_cuda(codes, "codes")
     m, k = codes.shape
     n = packed.shape[0]
@@ -105,11 +108,19 @@ def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_
     if want_accumulators:
         acc = torch.empty((m, n, k // 128 if group else 1), device=codes.device, dtype=torch.int32)
     lib = _lib.load_library()
-    fn = lib.sq_gemm_check if check_kernel else lib.sq_gemm
+    layout = int(codes_layout) | (_lib.CODES_INT4_RANGE if int4_range else 0)
     with torch.cuda.device(codes.device):
-        status = fn(codes.data_ptr(), int(codes_layout) | (_lib.CODES_INT4_RANGE if int4_range else 0), packed.data_ptr(), w_scales.data_ptr(),
-                    _wscale_mode(packed, w_scales), row_scales.data_ptr(), _ptr(bias),
-                    out.data_ptr(), _DTYPES[out_dtype], m, n, k, _ptr(acc), _stream())
+        if check_kernel or not split:
+            fn = lib.sq_gemm_check if check_kernel else lib.sq_gemm
+            status = fn(codes.data_ptr(), layout, packed.data_ptr(), w_scales.data_ptr(),
+                        _wscale_mode(packed, w_scales), row_scales.data_ptr(), _ptr(bias),
+                        out.data_ptr(), _DTYPES[out_dtype], m, n, k, _ptr(acc), _stream())
+        else:
+            scratch = torch.empty((max(lib.sq_split_workspace_bytes(m), 16),), device=codes.device, dtype=torch.uint8)
+            status = lib.sq_gemm_split(codes.data_ptr(), layout, packed.data_ptr(), w_scales.data_ptr(),
+                                       _wscale_mode(packed, w_scales), row_scales.data_ptr(), _ptr(bias),
+                                       out.data_ptr(), _DTYPES[out_dtype], m, n, k, _ptr(acc),
+                                       scratch.data_ptr(), scratch.numel(), _stream())
     _lib.check(status, "sq_gemm_check" if check_kernel else "sq_gemm")
     return (out, acc) if want_accumulators else out
 
@@ -152,9 +163,13 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
     lib = _lib.load_library()
     nbytes = lib.sq_workspace_bytes(rows, k)
     if workspace is None:
+        # room for the K-split scratch too (the kernel uses it when the tile count does not fill the SMs evenly)
+        nbytes += lib.sq_split_workspace_bytes(rows)
         workspace = torch.empty((max(nbytes, 1),), device=x.device, dtype=torch.uint8)
     elif workspace.numel() < nbytes or workspace.dtype != torch.uint8 or not workspace.is_cuda:
         raise RuntimeError("workspace must be a CUDA uint8 tensor of at least sq_workspace_bytes(rows, K) bytes.")
+    else:
+        nbytes = workspace.numel()
     if out is None:
         out = torch.empty((*x.shape[:-1], n), device=x.device, dtype=x.dtype)
     elif out.shape != (*x.shape[:-1], n) or out.dtype != x.dtype or not out.is_contiguous():
@@ -245,6 +260,15 @@ def mma_rate(n_cols: int = 128, iterations: int = 2000) -> float:
     _lib.check(status, "sq_mma_rate")
     torch.cuda.synchronize()
     return cycles.item() / (4.0 * iterations)
+
+
+def wait_probe(limit_us: int = 1000) -> int:
+    """Run ``sq_wait_probe``: a thread block waits ``limit_us`` microseconds for a barrier nobody arrives at and
+    gives up.  Returns the nanoseconds it waited (synchronises); ``device_status()`` afterwards reports 9190 once."""
+    waited = torch.zeros(1, device="cuda", dtype=torch.int64)
+    _lib.check(_lib.load_library().sq_wait_probe(int(limit_us), waited.data_ptr(), _stream()), "sq_wait_probe")
+    torch.cuda.synchronize()
+    return int(waited.item())
 
 
 def device_status() -> int:

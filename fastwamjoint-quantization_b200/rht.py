@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import hashlib
 import math
+from functools import lru_cache
 
 import torch
 
@@ -62,10 +63,98 @@ def randomized_block_hadamard_transform(values: torch.Tensor, signs: torch.Tenso
     return block_hadamard(values * signs.to(device=values.device, dtype=values.dtype), block)
 
 
+# Rows of the order-12 and order-28 Hadamard matrices the reference's "rht" rotation uses, one bit mask per row
+# (bit j set = +1 in column j).  The reference pins the same two tuples (``rht_constants.py:7-8``; they come from
+# the Hadamard tables of the QuaRot tooling, Apache-2.0): a rotated checkpoint is only meaningful with exactly
+# these matrices, so they are data of the format, like the nibble order of the packed weights.
+HAD12_MASKS = (1, 2955, 1815, 3629, 3163, 2231, 367, 733, 1465, 2929, 1763, 3525)
+HAD28_MASKS = (268419071, 185429047, 102422639, 204828893, 141222331, 14009207, 28002029, 55987673, 111958961,
+               223901537, 179367619, 90299783, 180583181, 92730907, 16382, 82979893, 165943403, 63484117, 126951851,
+               253887319, 239371949, 210341209, 152279729, 36156769, 72297155, 144577927, 20753165, 41489947)
+_OFFICIAL_ORDERS = {3072: 12, 14336: 28}
+MAX_BLOCK_IN_KERNEL = 256   # longest power-of-two rotation the pre-pass does inside a warp
+MAX_PART_IN_KERNEL = 512    # longest power-of-two part of its composite form
+
+
 def composite_order(width: int) -> int | None:
     """Order of the sign matrix the reference's "rht" rotation uses for this width (``rht.py:31-34``):
     12 at 3072, 28 at 14336, none for powers of two (plain FWHT)."""
-    return {3072: 12, 14336: 28}.get(int(width))
+    return _OFFICIAL_ORDERS.get(int(width))
+
+
+@lru_cache(maxsize=None)
+def official_hadamard_matrix(order: int) -> torch.Tensor:
+    """The order-12 / order-28 matrix of the reference (``rht.py:18-24``) as fp32 +-1 on the CPU."""
+    masks = {12: HAD12_MASKS, 28: HAD28_MASKS}[int(order)]
+    return torch.tensor([[1.0 if mask >> j & 1 else -1.0 for j in range(order)] for mask in masks])
+
+
+@lru_cache(maxsize=None)
+def sylvester_matrix(order: int) -> torch.Tensor:
+    """H_2 x ... x H_2 of a power-of-two order, entry (i, j) = (-1)^popcount(i & j)."""
+    if order < 1 or order & (order - 1):
+        raise ValueError("Sylvester matrices have power-of-two orders.")
+    index = torch.arange(order)
+    bits = index[:, None] & index[None, :]
+    parity = torch.zeros_like(bits)
+    while bool(bits.any()):
+        parity ^= bits & 1
+        bits = bits >> 1
+    return 1.0 - 2.0 * parity.float()
+
+
+def official_rotation_plan(width: int):
+    """How the reference's "rht" rotation of this width (``rht.py:27-39``) maps onto the pre-pass kernel:
+    ``("block", width)`` - one power-of-two transform over the whole row, done in a warp - or
+    ``("mix", matrix)`` - order x part with ``matrix`` across the parts: had12 x H256 at 3072, had28 x H512 at
+    14336, and H_(width/512) x H512 for the powers of two beyond a warp's reach (the same transform: a Sylvester
+    matrix factors into Sylvester matrices).  Other widths are refused with the reference's message."""
+    width = int(width)
+    if width > 0 and width & (width - 1) == 0:
+        if width <= MAX_BLOCK_IN_KERNEL:
+            return "block", width
+        part = min(width // 2, MAX_PART_IN_KERNEL)
+        if width // part > 32:
+            raise ValueError(f"Official FastWAM RHT of width {width} exceeds what the B200 pre-pass rotates (16384).")
+        return "mix", sylvester_matrix(width // part)
+    order = _OFFICIAL_ORDERS.get(width)
+    if order is None:
+        raise ValueError(f"Official FastWAM RHT supports power-of-two widths and 3072/14336, got {width}.")
+    return "mix", official_hadamard_matrix(order)
+
+
+_DEVICE_MATRICES: dict = {}
+
+
+def official_rotation_matrix(width: int, device) -> torch.Tensor | None:
+    """The ``mix`` matrix of ``official_rotation_plan`` on ``device`` (cached per width and device; call once
+    outside any CUDA-graph capture), or None when the plan is a plain block transform."""
+    kind, what = official_rotation_plan(width)
+    if kind == "block":
+        return None
+    key = (int(width), str(device))
+    if key not in _DEVICE_MATRICES:
+        _DEVICE_MATRICES[key] = what.to(device=device, dtype=torch.float32).contiguous()
+    return _DEVICE_MATRICES[key]
+
+
+def official_hadamard(values: torch.Tensor) -> torch.Tensor:
+    """``_official_hadamard`` of the reference (``rht.py:27-39``), forward direction: full-width normalised FWHT
+    for power-of-two widths, had12 / had28 across 256- / 512-long transformed parts at 3072 / 14336."""
+    width = int(values.shape[-1])
+    if width > 0 and width & (width - 1) == 0:
+        return block_hadamard(values, width)
+    order = _OFFICIAL_ORDERS.get(width)
+    if order is None:
+        raise ValueError(f"Official FastWAM RHT supports power-of-two widths and 3072/14336, got {width}.")
+    return composite_hadamard(values, official_hadamard_matrix(order))
+
+
+def randomized_official_hadamard_transform(values: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
+    """``rht_transform(values, signs, "rht")`` of the reference (``rht.py:56-66``)."""
+    if values.ndim == 0 or tuple(signs.shape) != (values.shape[-1],):
+        raise ValueError("Official RHT requires one sign per input channel.")
+    return official_hadamard(values * signs.to(device=values.device, dtype=values.dtype))
 
 
 def composite_hadamard(values: torch.Tensor, matrix: torch.Tensor) -> torch.Tensor:

@@ -12,12 +12,11 @@ Native buffers follow the deployment conventions (``runtime.py:88-92``, ``deploy
 ``weight`` packed uint8 [N, K/2], ``weight_scales`` fp32 [N], ``input_scale`` = 1/D, ``clipping_ranges`` =
 clip / qmax, ``gamma_gains`` [calls, streams], optional ``input_rotation_signs`` fp32 [K].
 
-Rotated sites: by default the rotation is block-local (``rotation_block``, the largest power of two
-dividing K capped at 256, or whatever the caller sets).  The reference's production rotation for
-K = 3072 / 14336 is the composite ``had12 x H256`` / ``had28 x H512`` (``rht.py:27-39``); it is selected by
-passing that order's sign matrix as ``rotation_matrix`` (the matrices belong to the checkpoint's tooling and
-are not part of this package).  Both backends of this class use the same rotation, so they agree with each
-other.
+Rotated sites (``rotation == "rht"``) use the reference's rotation for their width (``rht.py:27-39``): the
+full-width transform for powers of two, had12 x H256 at K = 3072, had28 x H512 at K = 14336; any other width
+is refused, as the reference refuses it.  ``rotation_block`` (a block-local power-of-two transform) and
+``rotation_matrix`` (a caller's own order x power-of-two composite) are explicit opt-ins for checkpoints that
+were rotated that way; nothing selects them by default.
 """
 from __future__ import annotations
 
@@ -29,7 +28,8 @@ import torch.nn.functional as F
 
 from .checkpoint import QuantizedSite
 from .quant import symmetric_fake_quant
-from .rht import randomized_block_hadamard_transform, randomized_composite_hadamard_transform, rht_block_size
+from .rht import (official_rotation_plan, randomized_block_hadamard_transform, randomized_composite_hadamard_transform,
+                  randomized_official_hadamard_transform)
 from .state import DenoiseCallState
 from .streams import FastWAMStreamConfig, expand_stream_gains, resolve_stream_layout
 from .topology import LinearSite, resolve_site_module, resolve_site_parent, stream_kind_of
@@ -39,8 +39,15 @@ _BUFFERS = ("weight", "weight_scales", "input_scale", "gamma_gains", "clipping_r
 # "rotation_matrix" is an optional extra buffer of rotated sites (see the module docstring)
 
 
-def default_rotation_block(width: int) -> int:
-    return min(rht_block_size(width), 256)
+def resolve_rotation(width: int, rotation_block, rotation_matrix):
+    """(block, matrix) a rotated site of this width hands to the kernels.  With neither opt-in given this is the
+    reference's rotation for the width (``official_rotation_plan``); widths it does not cover raise."""
+    if rotation_matrix is not None:
+        return 0, rotation_matrix
+    if rotation_block:
+        return int(rotation_block), None
+    kind, what = official_rotation_plan(width)
+    return (int(what), None) if kind == "block" else (0, what.clone())
 
 
 def _native_ops(activation_bits: int):
@@ -76,8 +83,15 @@ class WAMQuantLinear(nn.Module):
         self.supports_fused_gate_residual = False
         for name in _BUFFERS:
             self.register_buffer(name, tensors.get(name))
-        self.rotation_block = int(spec.get("rotation_block", default_rotation_block(self.weight.shape[1] * 2)))
-        self.register_buffer("rotation_matrix", tensors.get("rotation_matrix"))
+        self.official_rotation = False
+        self.rotation_block, matrix = 0, None
+        if rotation != "none":
+            self.official_rotation = not spec.get("rotation_block") and tensors.get("rotation_matrix") is None
+            self.rotation_block, matrix = resolve_rotation(self.weight.shape[1] * 2, spec.get("rotation_block"),
+                                                           tensors.get("rotation_matrix"))
+            if matrix is not None and self.weight.device.type != "meta":  # a meta build keeps it on the CPU until .to()
+                matrix = matrix.float().to(self.weight.device)
+        self.register_buffer("rotation_matrix", matrix, persistent=False)
         self.site = LinearSite(spec["site_index"], spec["expert"], -1, spec["operation"], spec["module_name"], None,
                                stream_kind_of(spec["operation"]))
         return self
@@ -102,7 +116,7 @@ class WAMQuantLinear(nn.Module):
         device = source.weight.device
         qmax = (1 << (activation_bits - 1)) - 1
         self.rotation = entry.rotation
-        self.rotation_block = int(rotation_block or default_rotation_block(entry.qweight.shape[1]))
+        self.official_rotation = rotated and not rotation_block and rotation_matrix is None
         signs = entry.input_rotation_signs
         self.register_buffer("input_rotation_signs", None if signs is None else signs.float().to(device))
         if rotation_matrix is not None:
@@ -113,8 +127,13 @@ class WAMQuantLinear(nn.Module):
                     or part > 512 or part & (part - 1)):
                 raise ValueError("rotation_matrix must be a square sign matrix whose order times a power of two "
                                  "(8..512) is the input width of a rotated site.")
+        self.rotation_block = 0
+        if rotated:
+            self.rotation_block, rotation_matrix = resolve_rotation(entry.qweight.shape[1], rotation_block, rotation_matrix)
+        if rotation_matrix is not None:
             rotation_matrix = rotation_matrix.float().to(device)
-        self.register_buffer("rotation_matrix", rotation_matrix)
+        # derived from the width (or given by the caller): not part of the state dict, whose keys stay the reference's
+        self.register_buffer("rotation_matrix", rotation_matrix, persistent=False)
         if native:
             ops = _native_ops(activation_bits)
             self._native_ops = ops
@@ -195,7 +214,10 @@ class WAMQuantLinear(nn.Module):
 
     def _reference_forward(self, x, call, layout):
         """Fake-quant forward of the reference (``runtime.py:155-175``), dividing order."""
-        if self.input_rotation_signs is not None and self.rotation_matrix is not None:
+        if self.input_rotation_signs is not None and self.official_rotation:
+            # rht_transform(x.float(), signs, "rht").to(x.dtype): the reference's own arithmetic (runtime.py:156-157)
+            x = randomized_official_hadamard_transform(x.float(), self.input_rotation_signs.to(x.device)).to(x.dtype)
+        elif self.input_rotation_signs is not None and self.rotation_matrix is not None:
             x = randomized_composite_hadamard_transform(x.float(), self.input_rotation_signs, self.rotation_matrix).to(x.dtype)
         elif self.input_rotation_signs is not None:
             x = randomized_block_hadamard_transform(x.float(), self.input_rotation_signs, self.rotation_block).to(x.dtype)

@@ -120,6 +120,23 @@ int sq_gemm(const void* codes, int codes_layout, const void* w_packed, const voi
             const float* row_scales, const void* bias, void* out, int out_dtype,
             int64_t M, int64_t N, int64_t K, int32_t* acc_dump, void* stream);
 
+/* sq_gemm with scratch for tiles that are split along K.  Whole output tiles (128 channels x up to 128 tokens)
+ * are dealt round-robin to one persistent thread block per SM; when the tile count is no multiple of the SM
+ * count - in particular with fewer tiles than SMs, the small-M regime of the reference (M = 32 ... 360,
+ * w4a8.cu:1038-1076 picks its tile shapes for it) - the remainder is cut into K ranges so that every SM gets the
+ * same number of 128-K blocks.  Each thread block parks its partial sums (fp32) in `split_workspace`; the one that
+ * arrives last at a tile adds them in K order (the result does not depend on the arrival order) and finishes the
+ * tile.  Integer accumulators are unchanged; group-form outputs differ from the unsplit kernel by fp32 rounding
+ * only, channel-form outputs not at all (the partial sums are exact integers).
+ *   split_workspace        16-byte aligned, sq_split_workspace_bytes(M) bytes, or null (then this is sq_gemm).
+ *                          Its first 1024 bytes are counters; this call puts a memset of them on `stream`.
+ * The reference has no counterpart: its CUTLASS GEMMs never split K. */
+int sq_gemm_split(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+                  const float* row_scales, const void* bias, void* out, int out_dtype,
+                  int64_t M, int64_t N, int64_t K, int32_t* acc_dump,
+                  void* split_workspace, size_t split_workspace_bytes, void* stream);
+size_t sq_split_workspace_bytes(int64_t M);
+
 /* Plain-CUDA-core version of sq_gemm with the same arguments (SQ_CODES_INT4_RANGE is accepted and ignored), the
  * same accumulators and, in the group form, the oracle's own fp32 summation order.  It exists so the
  * tensor-core kernel can be cross-checked on the device; it is not a fallback and nothing dispatches to it. */
@@ -145,7 +162,8 @@ int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled
 /* Profiling aid with no counterpart in the reference: one warp per SM issues `iterations` x 4
  * tcgen05.mma.kind::i8 (M = 128, N = n_cols in {64, 128, 256}, K = 32) back to back on fixed shared-memory tiles
  * and waits for them; `cycles` (device int64) receives thread block 0's SM cycles from first issue to
- * completion, so cycles / (4 * iterations) is the tensor pipe's time per MMA of that shape. */
+ * completion, so cycles / (4 * iterations) is the tensor pipe's time per MMA of that shape.  n_cols = 0x1000 + 128
+ * measures the N = 128 shape with operand A read from tensor memory instead of shared memory. */
 int sq_mma_rate(int n_cols, int iterations, long long* cycles, void* stream);
 
 /* Bytes of scratch one linear needs between sq_prepass and sq_gemm (codes + row scales), 256-byte rounded.
@@ -154,6 +172,8 @@ size_t sq_workspace_bytes(int64_t M, int64_t K);
 
 /* One whole linear: sq_prepass into `workspace`, then sq_gemm.  Same role as run_static_streams
  * (w4a8.cu:1337-1387, w4a4.cu:1517-1574) / symmetric_dynamic (w4a8.cu:1389-1452).
+ * A workspace of at least sq_workspace_bytes(rows, K) + sq_split_workspace_bytes(rows) bytes also lets the GEMM
+ * split tiles along K (see sq_gemm_split); the pre-pass clears the counters, so no memset is added.
  * `calls` and `call` select the schedule entry in static mode: act_scales [calls], gains [calls, streams];
  * an index outside [0, calls) is SQ_ERR_INDEX (w4a8.cu:1587-1628). */
 int sq_linear(const void* x, int x_dtype, int64_t rows, int64_t K, int64_t N, int abits, int mode,
@@ -248,6 +268,13 @@ int sq_linear_noalloc(const void* x, int x_dtype, int64_t rows, int64_t K, int64
                       int64_t span, int64_t streams, int64_t seq_tokens,
                       const void* w_packed, const void* w_scales, int wscale_mode, const void* bias,
                       void* out, void* stream);
+
+/* Test aid with no counterpart in the reference: proves that a wait which runs out ends as a status, not as a hung
+ * GPU.  One thread block allocates tensor memory, waits at most `limit_us` microseconds (1 ... 100000) on a barrier
+ * nobody ever arrives at - through the same bounded wait every pipeline role of sq_gemm uses, whose own limit is
+ * one second - then records status 9190, frees its tensor memory and returns; `waited_ns` (device int64, or
+ * null) receives how long it waited.  sq_device_status() then returns 9190 once, and the context stays usable. */
+int sq_wait_probe(int64_t limit_us, long long* waited_ns, void* stream);
 
 /* Reads (and clears) the device-side status word of the current device.  Kernels never spin forever:
  * a wait that exceeds its time limit records a code here and the kernel returns.  0 = no kernel gave up.

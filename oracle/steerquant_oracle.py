@@ -156,6 +156,32 @@ def composite_rotate(values: torch.Tensor, signs: torch.Tensor, matrix: torch.Te
     return composite_hadamard(values.float() * signs.float(), matrix)
 
 
+# Row masks of the reference's order-12 / order-28 sign matrices (bit j set = +1 in column j), as pinned in
+# ``rht_constants.py:7-8``; checked against matrices recorded from the reference (``tests/golden``).
+_HAD12_MASKS = (1, 2955, 1815, 3629, 3163, 2231, 367, 733, 1465, 2929, 1763, 3525)
+_HAD28_MASKS = (268419071, 185429047, 102422639, 204828893, 141222331, 14009207, 28002029, 55987673, 111958961,
+                223901537, 179367619, 90299783, 180583181, 92730907, 16382, 82979893, 165943403, 63484117, 126951851,
+                253887319, 239371949, 210341209, 152279729, 36156769, 72297155, 144577927, 20753165, 41489947)
+
+
+def official_matrix(order: int) -> torch.Tensor:
+    """``official_hadamard_matrix`` (``rht.py:18-24``)."""
+    masks = {12: _HAD12_MASKS, 28: _HAD28_MASKS}[order]
+    return torch.tensor([[1.0 if mask & (1 << j) else -1.0 for j in range(order)] for mask in masks])
+
+
+def official_rotate(values: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
+    """``rht_transform(values, signs, "rht")`` (``rht.py:27-39, 45-46, 61-63``): the width picks the transform -
+    one full-width normalised FWHT for a power of two, had12 x H256 at 3072, had28 x H512 at 14336."""
+    width = int(values.shape[-1])
+    signed = values.float() * signs.float()
+    if width > 0 and width & (width - 1) == 0:
+        return block_hadamard(signed, width)
+    if width not in (3072, 14336):
+        raise ValueError(f"Official FastWAM RHT supports power-of-two widths and 3072/14336, got {width}.")
+    return composite_hadamard(signed, official_matrix(12 if width == 3072 else 28))
+
+
 def rotate_weight(weight: torch.Tensor, signs: torch.Tensor, dtype: torch.dtype,
                   block: int = RHT_BLOCK) -> torch.Tensor:
     """Weight-side rotation: fp32 rotate, round to the model dtype

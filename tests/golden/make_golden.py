@@ -133,6 +133,41 @@ def main() -> None:
         out[f"mix{order}_out"] = rht.rht_transform(xin, signs_w, "rht").numpy()
         out[f"mix{order}_out_bf16"] = bits(rht.rht_transform(xin.bfloat16().float(), signs_w, "rht").to(torch.bfloat16))
 
+    # --- the reference CPU module on rotated sites whose rotation the width alone selects: had12 x H256 at
+    # 3072 (rht.py:31-39) and the full-width transform at 1024; appended last, with generators of their own, so
+    # the arrays above keep their values
+    for width in (3072, 1024):
+        wide_gen = torch.Generator(device="cpu").manual_seed(777 + width)
+        torch.manual_seed(7)
+        source = torch.nn.Linear(width, 8, bias=True, dtype=torch.bfloat16)
+        qweight = torch.randint(-7, 8, (8, width), generator=wide_gen, dtype=torch.int8)
+        wscale = torch.rand(8, 1, generator=wide_gen) * 0.01 + 0.002
+        dvec = torch.rand(width, generator=wide_gen) + 0.5
+        gains = torch.tensor([[0.5, 2.0], [2.0, 0.5]])
+        clips = torch.tensor([1.75, 3.5])
+        signs = rht.rht_signs(width, seed=42, module_name="linear")
+        entry = QuantizedSite(0, "linear", "action", "self_attn.o", ("action_chunk_0", "action_chunk_1"), qweight,
+                              wscale, dvec, gains, clips, torch.full((2, 2), 0.5), 0.0, 0.0, (0.0, 0.0), (0.0, 0.0),
+                              signs, "rht")
+        state = DenoiseCallState(2)
+        module = WAMQuantLinear(source, entry, state=state, stream_config=FastWAMStreamConfig(), weight_bits=4,
+                                activation_bits=4, backend="reference")
+        xin = (torch.randn(1, 6, width, generator=wide_gen) * 1.5).bfloat16()
+        tag = f"wide{width}"
+        for call in (0, 1):
+            state.set(call)
+            with torch.no_grad():
+                out[f"mod_{tag}_a4_call{call}_out_bf16"] = bits(module(xin))
+        out[f"mod_{tag}_x_bf16"] = bits(xin)
+        out[f"mod_{tag}_qweight"] = qweight.numpy()
+        out[f"mod_{tag}_wscale"] = wscale.numpy()
+        out[f"mod_{tag}_d"] = dvec.numpy()
+        out[f"mod_{tag}_gains"] = gains.numpy()
+        out[f"mod_{tag}_clips"] = clips.numpy()
+        out[f"mod_{tag}_bias_bf16"] = bits(source.bias.detach())
+        out[f"mod_{tag}_signs"] = signs.numpy()
+        out[f"rot_{tag}_out_bf16"] = bits(rht.rht_transform(xin.float(), signs, "rht").to(torch.bfloat16))
+
     np.savez_compressed(args.out, **out)
     print(f"wrote {args.out}: {len(out)} arrays, {Path(args.out).stat().st_size} bytes")
 

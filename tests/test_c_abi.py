@@ -61,3 +61,32 @@ def test_argument_errors_need_no_gpu(lib):
                             fake, fake, 0, None, fake, fake, 1 << 20, None) == lib.ERR_INDEX
     assert handle.sq_linear(fake, 0, 4, 256, 8, 4, 0, fake, None, 0, fake, fake, 10, 0, 2, 2, 4,
                             fake, fake, 0, None, fake, fake, 16, None) == lib.ERR_WORKSPACE
+
+
+def test_misaligned_pointers_are_rejected_on_the_host(lib):
+    """Every pointer a kernel reads or writes as a 16-byte vector is checked before anything is launched: a
+    pointer that is off by 4 bytes comes back as SQ_ERR_SHAPE instead of faulting on the device."""
+    handle = lib.load_library()
+    ok, off = ctypes.c_void_p(4096), ctypes.c_void_p(4096 + 4)
+    prepass = lambda x, inv_d, signs, codes: handle.sq_prepass(x, 0, 4, 256, 8, 1, inv_d, signs, 128, None, None, 1, 1,
+                                                               4, 0, 0, codes, ok, None)
+    assert prepass(off, None, None, ok) == lib.ERR_SHAPE      # x
+    assert prepass(ok, off, None, ok) == lib.ERR_SHAPE        # 1 / D
+    assert prepass(ok, None, off, ok) == lib.ERR_SHAPE        # signs
+    assert prepass(ok, None, None, off) == lib.ERR_SHAPE      # codes
+    gemm = lambda codes, packed, rows, out: handle.sq_gemm(codes, 1, packed, ok, 1, rows, None, out, 0, 4, 8, 256,
+                                                           None, None)
+    assert gemm(off, ok, ok, ok) == lib.ERR_SHAPE
+    assert gemm(ok, off, ok, ok) == lib.ERR_SHAPE
+    assert gemm(ok, ok, off, ok) == lib.ERR_SHAPE             # row scales are read four at a time
+    assert gemm(ok, ok, ok, off) == lib.ERR_SHAPE
+    # the fused entry: modulation rows and the norm weight
+    fused = lambda norm_weight, mod: handle.sq_linear_fused(
+        ok, 0, 4, 256, 8, 8, 1, None, None, 128, None, None, 0, 0, 1, 1, 4, ok, ok, 1, None,
+        0, 2, 1e-6, norm_weight, mod, mod, 1, 256, 0, 0, None, 1, 0, None, ok, ok, 1 << 20, None)
+    assert fused(off, None) == lib.ERR_SHAPE
+    assert fused(None, off) == lib.ERR_SHAPE
+    # K-split scratch of sq_gemm_split
+    assert handle.sq_gemm_split(ok, 1, ok, ok, 1, ok, None, ok, 0, 4, 8, 256, None, off, 1 << 20, None) == lib.ERR_SHAPE
+    assert handle.sq_split_workspace_bytes(0) == 0
+    assert handle.sq_split_workspace_bytes(16) >= 1024 + 2 * 16 * 128 * 4

@@ -189,6 +189,51 @@ def test_gemm_group_scheme(native, oracle, m, k, n, abits):
             assert rel_fro(out4.cpu(), want_out) < 2e-3
 
 
+@pytest.mark.parametrize("m,k,n", [(2048, 3072, 3072), (1024, 12288, 3072), (1100, 1024, 4096), (200, 3072, 3072),
+                                   (16, 3072, 12288)])
+@pytest.mark.parametrize("abits", [8, 4])
+def test_gemm_group_scheme_many_tiles(native, oracle, m, k, n, abits):
+    """Group form at sizes where a persistent thread block walks several tiles (more tiles than SMs: 384 at
+    2048 x 3072 x 3072, the benchmark's headline shape), with 96 groups per tile (K = 12288), with a ragged
+    last tile, and below one wave of tiles, where the tiles are split along K.  Every int32 accumulator of the
+    tensor-core kernel must equal the CUDA-core cross-check kernel's (itself pinned to the CPU oracle above),
+    with and without K-split scratch; a sample of rows is also recomputed by the CPU oracle (the reference's
+    exact-test bar, tests/test_wam_w4a4.py:32-58: atol = rtol = 0 on integers)."""
+    gen = torch.Generator().manual_seed(m + k + n + abits)
+    lim = 8 if abits == 4 else 128
+    codes = torch.randint(-lim + 1, lim, (m, k), generator=gen, dtype=torch.int8)
+    codes[0, :128] = -lim  # the most negative code the range allows, a whole group long
+    qweight = torch.randint(-8, 8, (n, k), generator=gen, dtype=torch.int8)
+    wscales = (torch.rand(n, k // 128, generator=gen) * 0.01 + 0.001).half()
+    row_scales = torch.rand(m, generator=gen) + 0.5
+    bias = (torch.randn(n, generator=gen) * 0.01).bfloat16()
+    packed = oracle.pack_signed_int4(qweight).cuda()
+    dev_codes = even_odd(codes).cuda()
+    args = (dev_codes, packed, wscales.cuda(), row_scales.cuda(), bias.cuda())
+    check_out, check_acc = native.gemm(*args, out_dtype=torch.bfloat16, want_accumulators=True, check_kernel=True)
+    rows = torch.arange(0, m, 37)
+    want_acc = torch.einsum("mgk,ngk->mng", codes[rows].view(len(rows), -1, 128).double(),
+                            qweight.view(n, -1, 128).double()).long()
+    assert torch.equal(check_acc[rows.cuda()].cpu().long(), want_acc)
+    want_out = oracle.epilogue_group(want_acc, wscales, row_scales[rows], bias, torch.bfloat16)
+    assert torch.equal(check_out[rows.cuda()].cpu().view(torch.int16), want_out.view(torch.int16))
+    for split in (False, True):
+        for int4_range in ((False, True) if abits == 4 else (False,)):
+            out, acc = native.gemm(*args, out_dtype=torch.bfloat16, want_accumulators=True, int4_range=int4_range,
+                                   split=split)
+            assert torch.equal(acc, check_acc), (split, int4_range)
+            # the drain sums the groups in fp32 in its own order: the bar grows with the number of groups
+            bar = 2e-3 if k <= 4096 else 4e-3
+            assert rel_fro(out[rows.cuda()].cpu(), want_out) < bar
+            assert rel_fro(out, check_out) < bar
+            plain = native.gemm(*args, out_dtype=torch.bfloat16, int4_range=int4_range, split=split)
+            assert torch.equal(plain, out)
+            again = native.gemm(*args, out_dtype=torch.bfloat16, int4_range=int4_range, split=split)
+            assert torch.equal(again, plain)  # the K-split reduction does not depend on arrival order
+            del out, acc
+    assert native.device_status() == 0
+
+
 @pytest.mark.parametrize("m,k,n", [(300, 3072, 384), (17, 256, 136), (520, 1024, 128), (2048, 1024, 512)])
 @pytest.mark.parametrize("group", [True, False])
 def test_prepacked_weights_give_the_same_bits(native, oracle, m, k, n, group):
@@ -335,6 +380,29 @@ def test_mma_rate_probe(native):
     assert native.device_status() == 0
     with pytest.raises(RuntimeError, match="enum"):
         native.mma_rate(96, 10)
+
+
+def test_a_wait_that_runs_out_becomes_a_status(native, oracle):
+    """The bounded wait of the pipeline roles, made to run out on purpose in the allowed way: a barrier nobody
+    arrives at, a limit of one millisecond.  The kernel returns, the status word names the wait, tensor memory
+    was released (a full 512-column GEMM right after gets its allocation and is exact), and the status is clear
+    again."""
+    assert native.device_status() == 0
+    waited = native.wait_probe(1000)
+    assert 1_000_000 <= waited < 50_000_000, waited
+    status = native.device_status()
+    lib = importlib.import_module("fastwamjoint_quantization_b200._lib")
+    assert status == 9190 and "wait probe" in lib.status_string(status)
+    assert native.device_status() == 0  # reading clears it
+    case = oracle.prepare_token_linear(300, 1024, 384, abits=8, seed=5)
+    want = oracle.linear_token(case["x"], case["qweight"], case["weight_scales"], case["bias"], abits=8, signs=None)
+    packed = oracle.pack_signed_int4(case["qweight"]).cuda()
+    _, acc = native.gemm(even_odd(want["codes"]).cuda(), packed, case["weight_scales"].cuda(),
+                         want["row_scales"].cuda(), None, out_dtype=torch.bfloat16, want_accumulators=True)
+    assert torch.equal(acc.cpu().long(), want["acc"])
+    assert native.device_status() == 0
+    with pytest.raises(RuntimeError, match="shape"):
+        native.wait_probe(0)
 
 
 def test_rejected_calls_raise(native, oracle):

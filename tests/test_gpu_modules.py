@@ -141,10 +141,11 @@ def test_rotated_native_module_against_its_reference_backend(m, oracle, k, n, ro
             actual, expected = native(x), reference(x)
             rel = (actual.float() - expected.float()).square().mean().sqrt() / expected.float().square().mean().sqrt()
             assert rel < 1e-2, float(rel)
-            want = oracle.linear_static(x.cpu(), entry.qweight, entry.weight_scales.reshape(-1), source.bias.detach().cpu(),
+            # no rotation option was given: the site's width selects the reference's rotation (rht.py:27-39)
+            rotated = oracle.official_rotate(x.cpu().float(), entry.input_rotation_signs).to(x.dtype)
+            want = oracle.linear_static(rotated, entry.qweight, entry.weight_scales.reshape(-1), source.bias.detach().cpu(),
                                         entry.input_scale.reciprocal(), entry.clipping_ranges / 7, entry.gamma_gains,
-                                        counts, call, abits=4, signs=entry.input_rotation_signs,
-                                        block=native.rotation_block)["out"]
+                                        counts, call, abits=4)["out"]
             rel = (actual.cpu().float() - want.float()).square().mean().sqrt() / want.float().square().mean().sqrt()
             assert rel < 0.003, float(rel)
             graph = torch.cuda.CUDAGraph()
@@ -178,8 +179,10 @@ def test_official_composite_rotation_module_and_graph(m, oracle, golden, dtype, 
     entry.gamma_gains[:] = (raw - (raw * entry.token_fractions[0]).sum()).exp()
     source = torch.nn.Linear(k, n, device="cuda", dtype=dtype)
     state = m["state"].DenoiseCallState(10)
+    # no rotation_matrix, no rotation_block: K = 3072 / 14336 alone selects had12 x H256 / had28 x H512
     module = R.WAMQuantLinear(source, entry, state=state, stream_config=m["streams"].FastWAMStreamConfig(),
-                              weight_bits=4, activation_bits=4, backend="cutlass_w4a4", rotation_matrix=matrix)
+                              weight_bits=4, activation_bits=4, backend="cutlass_w4a4")
+    assert module.official_rotation and torch.equal(module.rotation_matrix.cpu(), matrix)
     x = torch.randn(2 if rows == 129 else 1, rows, k, device="cuda", dtype=dtype)
 
     def expected(call):
@@ -209,6 +212,18 @@ def test_official_composite_rotation_module_and_graph(m, oracle, golden, dtype, 
     with pytest.raises(ValueError, match="block fusion"):
         R.WAMQuantLinear(source, entry, state=state, stream_config=m["streams"].FastWAMStreamConfig(), weight_bits=4,
                          activation_bits=4, backend="cutlass_w4a4", fuse_block=True, rotation_matrix=matrix)
+    # the operator called the way the reference's module calls it (positional, no rotation keyword) does the same
+    ops = importlib.import_module(P + "kernels.w4a4.wam_ops")
+    state.set(9)
+    with torch.inference_mode():
+        direct = ops.symmetric_scheduled_stream_rht_linear(
+            x, module.weight, module.weight_scales, module.bias, module.input_scale, module.clipping_ranges,
+            module.gamma_gains, counts, 9, module.input_rotation_signs)
+        torch.testing.assert_close(direct, module(x), atol=0, rtol=0)
+    # explicit opt-in to a block-local rotation still exists and is a different function of x
+    local = R.WAMQuantLinear(source, entry, state=state, stream_config=m["streams"].FastWAMStreamConfig(),
+                             weight_bits=4, activation_bits=4, backend="cutlass_w4a4", rotation_block=128)
+    assert not local.official_rotation and local.rotation_block == 128 and local.rotation_matrix is None
 
 
 class Tiny(torch.nn.Module):

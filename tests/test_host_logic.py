@@ -98,6 +98,35 @@ def test_reference_backend_module_matches_the_reference_package(mods, golden, ta
             assert torch.equal(got.view(torch.int16), want.view(torch.int16))
 
 
+@pytest.mark.parametrize("width", [3072, 1024])
+def test_rotated_site_takes_the_reference_rotation_for_its_width(mods, golden, width):
+    """A rotated site built WITHOUT a rotation matrix or block: the reference backend of this package must equal
+    outputs recorded from the reference's own module, which rotates with had12 x H256 at K = 3072 and with the
+    full-width transform at K = 1024 (rht.py:27-39).  A block-local default would fail both."""
+    R, St, Sm = mods["runtime"], mods["state"], mods["streams"]
+    tag = f"wide{width}"
+    source = torch.nn.Linear(width, 8, bias=True, dtype=torch.bfloat16)
+    with torch.no_grad():
+        source.bias.copy_(golden.bf16(f"mod_{tag}_bias"))
+    entry = _site(mods, golden, tag, True)
+    state = St.DenoiseCallState(2)
+    module = R.WAMQuantLinear(source, entry, state=state, stream_config=Sm.FastWAMStreamConfig(), weight_bits=4,
+                              activation_bits=4, backend="reference")
+    assert module.official_rotation
+    x = golden.bf16(f"mod_{tag}_x")
+    for call in (0, 1):
+        state.set(call)
+        want = golden.bf16(f"mod_{tag}_a4_call{call}_out")
+        assert torch.equal(module(x).view(torch.int16), want.view(torch.int16))
+    # what the native backend hands to the kernels for the same site
+    block, matrix = R.resolve_rotation(width, None, None)
+    assert block == 0 and matrix.shape == ((12, 12) if width == 3072 else (2, 2))
+    assert R.resolve_rotation(256, None, None) == (256, None)
+    assert R.resolve_rotation(3072, 128, None) == (128, None)  # explicit opt-in to a block-local rotation
+    with pytest.raises(ValueError, match="3072/14336"):
+        R.resolve_rotation(1536, None, None)
+
+
 def test_module_constructor_refusals(mods, golden):
     R, St, Sm = mods["runtime"], mods["state"], mods["streams"]
     source = torch.nn.Linear(256, 8, bias=False, dtype=torch.bfloat16)

@@ -1,5 +1,6 @@
 """The CPU oracle against outputs recorded from the reference package itself
 (``tests/golden/make_golden.py``).  Bit-exact unless a tolerance is written."""
+import pytest
 import torch
 
 
@@ -112,3 +113,20 @@ def test_accumulators_are_exact_integers(oracle):
     want = torch.einsum("mgk,ngk->mng", codes.reshape(9, 2, 128).long(), qweight.reshape(24, 2, 128).long())
     assert torch.equal(acc, want)
     assert torch.equal(oracle.group_accumulators(codes, qweight, None)[..., 0], want.sum(-1))
+
+
+def test_official_rotation_is_selected_by_the_width(oracle, golden):
+    """``official_rotate`` against the reference's ``rht_transform(..., "rht")``: matrices rebuilt from the masks,
+    full-width transform at 256 and 1024, had12 x H256 at 3072, had28 x H512 at 14336."""
+    for order in (12, 28):
+        assert torch.equal(oracle.official_matrix(order), golden[f"mix{order}_matrix"].float())
+    assert torch.equal(oracle.official_rotate(golden["rot_in"], golden["rot_signs"]), golden["rot_rht_out"])
+    for order, width in ((12, 3072), (28, 14336)):
+        signs = oracle.rht_signs(width, seed=42, module_name="linear")
+        assert torch.equal(oracle.official_rotate(golden[f"mix{order}_in"], signs), golden[f"mix{order}_out"])
+    for width in (3072, 1024):
+        x = golden.bf16(f"mod_wide{width}_x")
+        got = oracle.official_rotate(x.float(), golden[f"mod_wide{width}_signs"]).bfloat16()
+        assert torch.equal(got.view(torch.int16), golden.bf16(f"rot_wide{width}_out").view(torch.int16))
+    with pytest.raises(ValueError, match="3072/14336"):
+        oracle.official_rotate(torch.zeros(1, 1536), torch.ones(1536))
