@@ -58,19 +58,21 @@ int validate_gemm(const GemmArgs& a) {
 }
 
 // ------------------------------------------------------------------ kernel choice
-// SQ_GEMM_KERNEL=tc in the environment (read once) keeps the first-generation kernel for comparisons.
-static bool first_generation_requested() {
+// Two GEMM kernels share the interface.  sq_gemm_tc.cu (operands in shared memory, whole tiles only) is the
+// faster one at every size measured so far and is the default; SQ_GEMM_KERNEL=ts in the environment (read once)
+// selects sq_gemm_ts.cu (weights in tensor memory, tiles split along K) for comparisons.
+static bool second_generation_requested() {
   static const bool requested = [] {
     const char* value = std::getenv("SQ_GEMM_KERNEL");
-    return value != nullptr && std::strcmp(value, "tc") == 0;
+    return value != nullptr && std::strcmp(value, "ts") == 0;
   }();
   return requested;
 }
 
-bool gemm_takes_split_workspace(const GemmArgs& a) { return !a.weights_prepacked && !first_generation_requested(); }
+bool gemm_takes_split_workspace(const GemmArgs& a) { return !a.weights_prepacked && second_generation_requested(); }
 
 int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
-  if (a.weights_prepacked || first_generation_requested()) return launch_gemm_tc(a, stream);
+  if (a.weights_prepacked || !second_generation_requested()) return launch_gemm_tc(a, stream);
   return launch_gemm_ts(a, stream);
 }
 
@@ -286,8 +288,8 @@ int sq_gemm_timeline(const void* codes, const void* w_packed, const void* w_scal
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K, long long* timeline, void* stream) {
   const sq::GemmArgs a = make_args(codes, SQ_CODES_EVEN_ODD | SQ_CODES_INT4_RANGE, w_packed, w_scales,
                                    SQ_WSCALE_GROUP_F16, row_scales, bias, out, SQ_BF16, M, N, K, nullptr);
-  if (sq::first_generation_requested()) return sq::launch_gemm_timeline(a, timeline, static_cast<cudaStream_t>(stream));
-  return sq::launch_gemm_ts_timeline(a, timeline, static_cast<cudaStream_t>(stream));
+  if (sq::second_generation_requested()) return sq::launch_gemm_ts_timeline(a, timeline, static_cast<cudaStream_t>(stream));
+  return sq::launch_gemm_timeline(a, timeline, static_cast<cudaStream_t>(stream));
 }
 
 int sq_prepack_weights(const void* w_packed, int64_t N, int64_t K, void* w_tiled, void* stream) {

@@ -98,6 +98,7 @@ struct TcParams {
   int offset_steps;     // group mode: constant-tile MMAs in front of every group (1 or 4)
   uint32_t offset_word;  // four copies of the constant tile's byte
   uint32_t offset_bits;  // what those MMAs add to every accumulator element
+  uint32_t offset_unsigned;  // the offset MMA multiplies unsigned bytes
   int out_dtype;
   // fused epilogue: out = residual + gate * act(linear)
   int activation;
@@ -320,7 +321,9 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             tc_fence_after_sync();
             if (elect_one()) {
               const uint64_t desc_c = umma_desc_k128(c_tile);
-              for (int b = 0; b < p.offset_steps; ++b) umma_i8(tmem_d, desc_c, desc_c, idesc, b > 0 ? 1u : 0u);
+              // codes of any int8 value: ONE unsigned x unsigned MMA of 0xFF bytes adds 32 * 255 * 255, which covers
+              // the most negative group sum (16 * 8 * 127 * 128); codes within [-8, 7]: one signed MMA of 0x40 bytes
+              umma_i8(tmem_d, desc_c, desc_c, p.offset_unsigned != 0 ? umma_idesc_u8(kBlockCh, umma_n) : idesc, 0u);
             }
             __syncwarp();
           }
@@ -451,12 +454,20 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       for (int i = 0; i < (kGroup ? 1 : kCols); ++i) sums[i] = 0.0f;
       float offset_sum = 0.0f;  // what the constant offsets added to every sum of this channel
 
-      // group scales are fetched two groups ahead as raw fp16 bits and converted when used, so the
-      // global-load latency never sits in front of a drain
-      unsigned short raw0 = 0, raw1 = 0;
-      if (kGroup && n_ok) {
-        raw0 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups);
-        if (groups > 1) raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + 1);
+      // Group scales: chunks of eight (one 16-byte load), the next chunk requested a whole chunk ahead, so no global
+      // load latency sits on the per-group path; other group counts use scalar loads two groups ahead.
+      const unsigned short* my_scales = reinterpret_cast<const unsigned short*>(scale_row) + (n_ok ? n : 0) * groups;
+      const bool scale_vectors = kGroup && (groups & 7) == 0 && (reinterpret_cast<uintptr_t>(p.w_scales) & 15u) == 0;
+      uint4 chunk = make_uint4(0u, 0u, 0u, 0u), chunk_next = make_uint4(0u, 0u, 0u, 0u);
+      unsigned short raw_a = 0, raw_b = 0;
+      if (kGroup) {
+        if (scale_vectors) {
+          chunk = __ldg(reinterpret_cast<const uint4*>(my_scales));
+          if (groups > 8) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + 1);
+        } else {
+          raw_a = __ldg(my_scales);
+          if (groups > 1) raw_b = __ldg(my_scales + 1);
+        }
       }
 
       for (int g = 0; g < groups && ok; ++g, ++git) {
@@ -466,11 +477,25 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const bool split = !kGroup && p.mma_split == 2;
         float scale = 0.0625f;  // the unpacked weights are 16 x the int4 value
         if (kGroup) {
-          scale = __half2float(__ushort_as_half(raw0)) * kScaleUp;
+          unsigned short raw;
+          if (scale_vectors) {
+            const int e = g & 7;
+            const uint32_t word = e < 4 ? (e < 2 ? chunk.x : chunk.y) : (e < 6 ? chunk.z : chunk.w);
+            raw = static_cast<unsigned short>((e & 1) != 0 ? word >> 16 : word & 0xFFFFu);
+            if (e == 7) {
+              chunk = chunk_next;
+              const int c2 = (g >> 3) + 2;
+              if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+            }
+          } else {
+            raw = (g & 1) == 0 ? raw_a : raw_b;
+            if (g + 2 < groups) {
+              const unsigned short ahead = __ldg(my_scales + g + 2);
+              if ((g & 1) == 0) raw_a = ahead; else raw_b = ahead;
+            }
+          }
+          scale = __half2float(__ushort_as_half(raw)) * kScaleUp;
           offset_sum = fmaf(offset_float, scale, offset_sum);
-          raw0 = raw1;
-          if (g + 2 < groups && n_ok)
-            raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + g + 2);
         }
         if (!mbar_wait_bounded(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9005);
@@ -698,9 +723,9 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
     p.slice_cols = want < cap ? want : cap;
     p.mma_split = (a.K + kBlockK - 1) / kBlockK >= 2 ? 2 : 1;
     if (a.codes_int4_range) {
-      p.offset_steps = 1; p.offset_word = 0x40404040u; p.offset_bits = 1u << 17;
+      p.offset_steps = 1; p.offset_word = 0x40404040u; p.offset_bits = 1u << 17; p.offset_unsigned = 0u;
     } else {
-      p.offset_steps = 4; p.offset_word = 0x80808080u; p.offset_bits = 1u << 21;
+      p.offset_steps = 1; p.offset_word = 0xFFFFFFFFu; p.offset_bits = 32u * 255u * 255u; p.offset_unsigned = 1u;
     }
   }
   p.tok_tiles = static_cast<int>((a.M + tok_tile - 1) / tok_tile);

@@ -10,7 +10,7 @@
 //     (8 KiB in, 8 KiB read once) and the codes (16 KiB in, 16 KiB read by the tensor core) instead of also a
 //     16 KiB unpacked tile written and read: a 128 x 128 x 32 MMA with both operands in shared memory needs
 //     the full 128 B/clk of the shared-memory port for itself.
-//   * Eight "fat" drain warps (two per TMEM lane quarter, 64 token columns each, 224 registers) keep TWO
+//   * Eight "fat" drain warps (two per TMEM lane quarter, 64 token columns each, 200 registers) keep TWO
 //     accumulators in flight: the tcgen05.ld of group g + 1 is issued before the FFMAs of group g, so the
 //     barrier / TMEM round trips of one group hide behind the arithmetic of the previous one.
 //   * Work is cut into (tile, K-range) items.  Whole tiles go round-robin over the persistent CTAs; what is
@@ -46,13 +46,13 @@ namespace {
 constexpr int kBlockCh = 128;  // output channels per tile = UMMA M = TMEM lanes
 constexpr int kBlockK = 128;   // int8 K elements per stage = one swizzle row = one weight group
 constexpr int kUmmaK = 32;     // K of one kind::i8 instruction
-constexpr int kThreads = 512;
+constexpr int kThreads = 768;
 constexpr int kUnpackWarps = 4;
-constexpr int kDrainWarps = 8;
-constexpr int kRegsControl = 32, kRegsUnpack = 32, kRegsDrain = 224;
+constexpr int kDrainWarps = 16;
+constexpr int kRegsControl = 32, kRegsUnpack = 32, kRegsDrain = 104;
 // setmaxnreg.inc only hands out registers the CTA was launched with: the launcher checks this sum against
 // (registers per thread at launch) x kThreads before every launch.
-constexpr int kRegisterPoolNeeded = 128 * kRegsControl + 128 * kRegsUnpack + 256 * kRegsDrain;
+constexpr int kRegisterPoolNeeded = 128 * kRegsControl + 128 * kRegsUnpack + 512 * kRegsDrain;
 constexpr uint32_t kPackedBytes = kBlockCh * kBlockK / 2;  // 8 KiB
 constexpr uint32_t kConstTileBytes = kBlockCh * kBlockK;   // 16 KiB: both operands of the offset MMA
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
@@ -63,8 +63,10 @@ constexpr uint32_t kAStages = 4;       // unpacked-weight ring in TMEM
 constexpr uint32_t kAStageCols = 32;   // 128 K bytes per lane
 constexpr uint32_t kAColBase = kAccBufs * kAccStride;  // 384
 constexpr uint32_t kTmemCols = 512;
-constexpr int kStages = 8;             // shared-memory ring (packed weights + codes)
 constexpr int kRowScaleSlots = 2;
+// shared-memory ring (packed weights + codes): what is left next to the constant tile and the output staging
+__host__ __device__ constexpr int stages_for(int tok) { return tok == 128 ? 8 : 10; }
+
 
 // Group mode keeps every accumulator positive (see sq_gemm_tc.cu): a positive int32 below 2^23 read as a float is
 // the denormal acc * 2^-149, so the drain is one packed FFMA per two elements with the scale pre-multiplied.
@@ -73,11 +75,12 @@ constexpr float kScaleDown = 562949953421312.0f;   // 2^49 = 2^149 / 2^96 / 16 (
 
 constexpr int kTraceSlots = 512;
 enum TraceRole { kTrTmaIssue = 0, kTrConvStart, kTrConvDone, kTrMmaAccFree, kTrMmaIssue, kTrDrainStart,
-                 kTrDrainRelease, kTrDrainDone, kTrMmaCommitted, kTraceRoles };
+                 kTrDrainRelease, kTrDrainDone, kTrMmaCommitted, kTrDrainTop, kTrDrainLoaded, kTrItemEnd, kTraceRoles };
 
 __host__ __device__ constexpr uint32_t stage_bytes(int tok) { return tok * kBlockK + kPackedBytes; }
 __host__ __device__ constexpr uint32_t smem_bytes_for(int tok) {
-  return kStages * stage_bytes(tok) + kConstTileBytes + kRowScaleSlots * 512 + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  return stages_for(tok) * stage_bytes(tok) + kConstTileBytes + kRowScaleSlots * 512 +
+         1024 /*alignment slack*/ + 512 /*barriers*/;
 }
 
 // How the tiles are dealt to the CTAs.  Tiles [0, tail_first) are whole items: tile = round * grid + cta.
@@ -207,9 +210,9 @@ template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool k
 __global__ void __launch_bounds__(kThreads, 1)
 sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TsParams p) {
-  constexpr int S = kStages;
+  constexpr int S = stages_for(TOK);
   constexpr uint32_t kXBytes = TOK * kBlockK;
-  constexpr int kCols = TOK / 2;  // token columns per drain warp: 64, 32 or 16
+  constexpr int kCols = TOK / 4 < 16 ? 16 : TOK / 4;  // token columns per drain warp: 32 or 16
   static_assert(TOK == 128 || TOK == 64 || TOK == 32, "tile capacities");
 
   extern __shared__ uint8_t smem_raw[];
@@ -281,6 +284,13 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const Plan& pl = p.plan;
+  const uint32_t wait_kind = (p.flags >> 3) & 3u;  // experiment switch: how a role waits on a barrier
+  auto wait_on = [&](uint32_t bar, uint32_t parity, volatile int* flag, uint64_t limit) {
+    if (wait_kind == 1u) return mbar_wait_bounded(bar, parity, flag, limit);
+    if (wait_kind == 2u) return mbar_wait_probe<32>(bar, parity, flag, limit);
+    if (wait_kind == 3u) return mbar_wait_probe<0>(bar, parity, flag, limit);
+    return mbar_wait_light(bar, parity, flag, limit);
+  };
   const bool tracing = kTrace && blockIdx.x == 0 && p.timeline != nullptr;
   auto stamp = [&](int role, uint32_t slot) {
     if (kTrace && tracing && slot < kTraceSlots) p.timeline[role * kTraceSlots + slot] = clock64();
@@ -301,7 +311,7 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const int tok0 = (item.tile / pl.ch_tiles) * p.tok_tile;
         for (int g = item.g0; g < item.g1; ++g, ++it) {
           const uint32_t s = it % S, phase = (it / S) & 1u;
-          if (!mbar_wait_bounded(bar_x_empty + 8 * s, phase ^ 1u, abort_flag, kWaitLimitNs)) {
+          if (!wait_on(bar_x_empty + 8 * s, phase ^ 1u, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9101);
             ok = false;
             break;
@@ -317,7 +327,7 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         }
         if (!ok) break;
         const uint32_t slot = item_idx % kRowScaleSlots, rphase = (item_idx / kRowScaleSlots) & 1u;
-        if (!mbar_wait_bounded(bar_rs_empty + 8 * slot, rphase ^ 1u, abort_flag, kWaitLimitNs)) {
+        if (!wait_on(bar_rs_empty + 8 * slot, rphase ^ 1u, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9107);
           break;
         }
@@ -359,7 +369,7 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (!kGroup) {
           buf = item_idx % kAccBufs;
           const uint32_t aphase = (item_idx / kAccBufs) & 1u;
-          if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aphase ^ 1u, abort_flag, kWaitLimitNs)) {
+          if (!wait_on(bar_acc_empty + 8 * buf, aphase ^ 1u, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9102);
             break;
           }
@@ -369,7 +379,7 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             if (it % kAccBufs != mine) continue;
             buf = mine;
             const uint32_t aphase = (it / kAccBufs) & 1u;
-            if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aphase ^ 1u, abort_flag, kWaitLimitNs)) {
+            if (!wait_on(bar_acc_empty + 8 * buf, aphase ^ 1u, abort_flag, kWaitLimitNs)) {
               if (lane == 0) report_timeout(p.status, abort_flag, 9102);
               ok = false;
               break;
@@ -388,8 +398,8 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           }
           const uint32_t s = it % S, sphase = (it / S) & 1u;
           const uint32_t ta = it % kAStages, tphase = (it / kAStages) & 1u;
-          if (!mbar_wait_bounded(bar_a_full + 8 * ta, tphase, abort_flag, kWaitLimitNs) ||
-              !mbar_wait_bounded(bar_full_x + 8 * s, sphase, abort_flag, kWaitLimitNs)) {
+          if (!wait_on(bar_a_full + 8 * ta, tphase, abort_flag, kWaitLimitNs) ||
+              !wait_on(bar_full_x + 8 * s, sphase, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9103);
             ok = false;
             break;
@@ -433,11 +443,11 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       for (int g = item.g0; g < item.g1; ++g, ++it) {
         const uint32_t s = it % S, phase = (it / S) & 1u;
         const uint32_t ta = it % kAStages;
-        bool ready = mbar_wait_bounded(bar_full_p + 8 * s, phase, abort_flag, kWaitLimitNs);
+        bool ready = wait_on(bar_full_p + 8 * s, phase, abort_flag, kWaitLimitNs);
         if (ready && it >= kAStages) {
           // the TMEM stage is free when the MMAs of iteration it - kAStages have retired
           const uint32_t j = it - kAStages;
-          ready = mbar_wait_bounded(bar_x_empty + 8 * (j % S), (j / S) & 1u, abort_flag, kWaitLimitNs);
+          ready = wait_on(bar_x_empty + 8 * (j % S), (j / S) & 1u, abort_flag, kWaitLimitNs);
         }
         if (!ready) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9104);
@@ -501,17 +511,18 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   } else {
     // ------------------------------------------------------------------ drain warpgroups
     reg_inc<kRegsDrain>();
-    const int dwarp = warp - 8;            // 0..7
+    const int dwarp = warp - 8;            // 0..15
     const int quarter = warp & 3;          // TMEM lane quarter this warp may address
-    const int half = dwarp >> 2;           // which half of the token columns
+    const int slice = dwarp >> 2;          // which slice of the token columns (four warps per lane quarter)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int ch_in_tile = quarter * 32 + lane;
-    const int my_col0 = half * kCols;
-    const __half* scale_row = static_cast<const __half*>(p.w_scales);
+    const int my_col0 = slice * kCols;
+    const unsigned short* scale_bits = static_cast<const unsigned short*>(p.w_scales);
     const uint32_t offset_bits = kGroup ? p.offset_bits : 0u;
     const float offset_float = __uint_as_float(offset_bits);
     const int groups = pl.groups;
-
+    // eight group scales of a channel are one 16-byte load when the rows of the scale matrix allow it
+    const bool scale_vectors = kGroup && (groups & 7) == 0 && (reinterpret_cast<uintptr_t>(p.w_scales) & 15u) == 0;
     ItemIter iter;
     iter.init(pl, cta);
     Item item;
@@ -533,73 +544,84 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       float offset_sum = 0.0f;  // what the constant offsets added to every sum of this channel
 
       if (kGroup) {
-        // group scales are fetched two groups ahead as raw fp16 bits and converted when used
-        unsigned short raw0 = 0, raw1 = 0;
-        if (n_ok) {
-          raw0 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + item.g0);
-          if (n_groups > 1) raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + item.g0 + 1);
+        // Group scales: chunks of eight (one uint4), the next chunk requested a whole chunk ahead, so no global
+        // load latency sits on the per-group path.  Scalar loads (other group counts) are requested two groups ahead.
+        const unsigned short* my_scales = scale_bits + (n_ok ? n : 0) * groups;
+        uint4 chunk = make_uint4(0u, 0u, 0u, 0u), chunk_next = make_uint4(0u, 0u, 0u, 0u);
+        unsigned short raw_a = 0, raw_b = 0;
+        if (scale_vectors) {
+          const int c0 = item.g0 >> 3;
+          chunk = __ldg(reinterpret_cast<const uint4*>(my_scales) + c0);
+          if (8 * (c0 + 1) < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c0 + 1);
+        } else {
+          raw_a = __ldg(my_scales + item.g0);
+          if (n_groups > 1) raw_b = __ldg(my_scales + item.g0 + 1);
         }
-        uint32_t ra[kCols], rb[kCols];
-        // one step: group i's accumulator sits in `cur` (load issued earlier); release it, start the load of
-        // group i + 1 into `nxt`, then do group i's arithmetic while that load is in flight
-        auto step = [&](uint32_t (&cur)[kCols], uint32_t (&nxt)[kCols], int i) -> bool {
-          const float scale = __half2float(__ushort_as_half(raw0)) * kScaleUp;
+        // per group: wait for the accumulator, one wide TMEM load, hand the accumulator back, then the arithmetic
+        // (a load takes about a hundred cycles; the two drain warps of a scheduler overlap each other's loads
+        // and FFMAs, keeping a second load in flight per warp measured no faster)
+        for (int i = 0; i < n_groups; ++i) {
+          const int g = item.g0 + i;
+          if (threadIdx.x == 256) stamp(kTrDrainTop, it + static_cast<uint32_t>(i));
+          unsigned short raw;
+          if (scale_vectors) {
+            const int e = g & 7;
+            const uint32_t word = e < 4 ? (e < 2 ? chunk.x : chunk.y) : (e < 6 ? chunk.z : chunk.w);
+            raw = static_cast<unsigned short>((e & 1) != 0 ? word >> 16 : word & 0xFFFFu);
+            if (e == 7) {
+              chunk = chunk_next;
+              const int c2 = (g >> 3) + 2;
+              if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+            }
+          } else {
+            raw = (i & 1) == 0 ? raw_a : raw_b;
+            if (i + 2 < n_groups) {
+              const unsigned short ahead = __ldg(my_scales + g + 2);
+              if ((i & 1) == 0) raw_a = ahead; else raw_b = ahead;
+            }
+          }
+          const float scale = __half2float(__ushort_as_half(raw)) * kScaleUp;
           offset_sum = fmaf(offset_float, scale, offset_sum);
-          raw0 = raw1;
-          if (i + 2 < n_groups && n_ok)
-            raw1 = __ldg(reinterpret_cast<const unsigned short*>(scale_row) + n * groups + item.g0 + i + 2);
           const uint32_t git = it + static_cast<uint32_t>(i);
-          tmem_wait_ld();  // `cur` is valid
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * (git % kAccBufs));
-          if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
-          if (i + 1 < n_groups) {
-            const uint32_t nb = (git + 1) % kAccBufs, nphase = ((git + 1) / kAccBufs) & 1u;
-            if (!mbar_wait_bounded(bar_acc_full + 8 * nb, nphase, abort_flag, kWaitLimitNs)) {
-              if (lane == 0) report_timeout(p.status, abort_flag, 9105);
-              return false;
-            }
-            tc_fence_after_sync();
-            if (my_cols > 0) tmem_ld_chunk(tmem_base + lane_addr + nb * kAccStride + my_col0, nxt);
-          }
-          if (my_cols > 0) {
-            const uint64_t scale2 = pack2(scale, scale);
-#pragma unroll
-            for (int c = 0; c < kCols; c += 2) ffma2(sums2[c / 2], cur[c], cur[c + 1], scale2);
-            if (kDump) {
-#pragma unroll
-              for (int c = 0; c < kCols; ++c) {
-                if (n_ok && c < my_cols) {
-                  const int64_t m = tok0 + my_col0 + c;
-                  p.acc_dump[(m * p.N + n) * groups + item.g0 + i] = static_cast<int32_t>(cur[c] - offset_bits) >> 4;
-                }
-              }
-            }
-          }
-          if (threadIdx.x == 256) stamp(kTrDrainDone, git);
-          return true;
-        };
-        {
-          const uint32_t b0 = it % kAccBufs, phase0 = (it / kAccBufs) & 1u;
-          if (!mbar_wait_bounded(bar_acc_full + 8 * b0, phase0, abort_flag, kWaitLimitNs)) {
+          const uint32_t buf = git % kAccBufs, aphase = (git / kAccBufs) & 1u;
+          if (!wait_on(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9105);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          if (threadIdx.x == 256) stamp(kTrDrainStart, it);
-          if (my_cols > 0) tmem_ld_chunk(tmem_base + lane_addr + b0 * kAccStride + my_col0, ra);
-        }
-        for (int i = 0; i < n_groups && ok; i += 2) {
-          ok = step(ra, rb, i);
-          if (ok && i + 1 < n_groups) ok = step(rb, ra, i + 1);
+          if (threadIdx.x == 256) stamp(kTrDrainStart, git);
+          uint32_t r[kCols];
+          if (my_cols > 0) {
+            tmem_ld_chunk(tmem_base + lane_addr + buf * kAccStride + my_col0, r);
+            tmem_wait_ld();
+          }
+          if (threadIdx.x == 256) stamp(kTrDrainLoaded, git);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+          if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
+          if (my_cols > 0) {
+            const uint64_t scale2 = pack2(scale, scale);
+#pragma unroll
+            for (int c = 0; c < kCols; c += 2) ffma2(sums2[c / 2], r[c], r[c + 1], scale2);
+            if (kDump) {
+              for (int c = 0; c < my_cols; ++c) {
+                uint32_t v = 0;
+#pragma unroll
+                for (int k = 0; k < kCols; ++k) v = k == c ? r[k] : v;
+                const int64_t m = tok0 + my_col0 + c;
+                if (n_ok) p.acc_dump[(m * p.N + n) * groups + g] = static_cast<int32_t>(v - offset_bits) >> 4;
+              }
+            }
+          }
+          if (threadIdx.x == 256) stamp(kTrDrainDone, git);
         }
         if (!ok) break;
         it += static_cast<uint32_t>(n_groups);
       } else {
         const uint32_t buf = item_idx % kAccBufs, aphase = (item_idx / kAccBufs) & 1u;
-        if (!mbar_wait_bounded(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
+        if (!wait_on(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9105);
           ok = false;
           break;
@@ -620,28 +642,81 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             sums2[c / 2] = pack2(static_cast<float>(static_cast<int32_t>(r[c])) * 0.0625f,
                                  static_cast<float>(static_cast<int32_t>(r[c + 1])) * 0.0625f);
           }
-          if (kDump) {
-            const bool whole = item.g0 == 0 && item.g1 == groups;
-#pragma unroll
-            for (int c = 0; c < kCols; ++c) {
-              if (n_ok && c < my_cols) {
-                const int64_t m = tok0 + my_col0 + c;
-                const int32_t v = static_cast<int32_t>(r[c]) >> 4;
-                if (whole) p.acc_dump[m * p.N + n] = v;
-                else atomicAdd(p.acc_dump + m * p.N + n, v);  // the launcher cleared the dump
-              }
-            }
-          }
         }
       }
 
       // ---------------------------------------------------------------- end of the item
+      // Straight-line code over this warp's (at most 32) columns: every column is independent, so the loads,
+      // the arithmetic and the stores of different columns overlap.
       const bool whole = item.g0 == 0 && item.g1 == groups;
-      bool finalize = whole;
+      const uint32_t rslot = item_idx % kRowScaleSlots, rphase = (item_idx / kRowScaleSlots) & 1u;
+      if (!wait_on(bar_rs_full + 8 * rslot, rphase, abort_flag, kWaitLimitNs)) {
+        if (lane == 0) report_timeout(p.status, abort_flag, 9109);
+        ok = false;
+        break;
+      }
+      if (threadIdx.x == 256) stamp(kTrItemEnd, 8 * item_idx);
+      float wscale = 1.0f;
+      if (!kGroup && n_ok) wscale = __ldg(static_cast<const float*>(p.w_scales) + n);
+      const bool has_bias = p.bias != nullptr && n_ok;
+      const float bias = has_bias ? to_float<OutT>(__ldg(static_cast<const OutT*>(p.bias) + n)) : 0.0f;
+      const float* row_scale = reinterpret_cast<const float*>(smem_gen + (rs_base - smem_base)) + rslot * 128 + my_col0;
+      // one output element: row scale, weight scale, bias, gate, residual, one rounding to the output type
+      auto emit = [&](float v, float rs, int col) {
+        float y = kGroup ? __fmul_rn(v, __fmul_rn(rs, kScaleDown)) : __fmul_rn(__fmul_rn(v, rs), wscale);
+        if (has_bias) y = __fadd_rn(y, bias);
+        const int64_t m = tok0 + my_col0 + col;
+        if (n_ok) {
+          // gate and residual: a separate multiply and add, each rounded, as an unfused epilogue would
+          if (p.gate != nullptr)
+            y = __fmul_rn(y, to_float<OutT>(__ldg(static_cast<const OutT*>(p.gate) + (m / p.gate_span) * p.gate_row_stride + n)));
+          if (p.residual != nullptr)
+            y = __fadd_rn(y, to_float<OutT>(__ldg(static_cast<const OutT*>(p.residual) + m * p.N + n)));
+          static_cast<OutT*>(p.out)[m * p.N + n] = from_float<OutT>(y);
+        }
+      };
+      if (whole) {
+#pragma unroll
+        for (int c = 0; c < kCols; c += 4) {
+          if (c < my_cols) {
+            const float4 rs = *reinterpret_cast<const float4*>(row_scale + c);
+            const float2 lo = unpack2(sums2[c / 2]), hi = unpack2(sums2[c / 2 + 1]);
+            emit(__fsub_rn(lo.x, offset_sum), rs.x, c);
+            if (c + 1 < my_cols) emit(__fsub_rn(lo.y, offset_sum), rs.y, c + 1);
+            if (c + 2 < my_cols) emit(__fsub_rn(hi.x, offset_sum), rs.z, c + 2);
+            if (c + 3 < my_cols) emit(__fsub_rn(hi.y, offset_sum), rs.w, c + 3);
+          }
+        }
+      }
+      if (kDump && !kGroup && my_cols > 0) {  // channel form: the item's integer sum (exact in fp32: |sum| < 2^24)
+        for (int c = 0; c < my_cols; ++c) {
+          float v = 0.0f;
+#pragma unroll
+          for (int k = 0; k < kCols; ++k) {
+            const float2 pair = unpack2(sums2[k / 2]);
+            v = k == c ? ((k & 1) != 0 ? pair.y : pair.x) : v;
+          }
+          const int64_t m = tok0 + my_col0 + c;
+          if (n_ok) {
+            if (whole) p.acc_dump[m * p.N + n] = static_cast<int32_t>(v);
+            else atomicAdd(p.acc_dump + m * p.N + n, static_cast<int32_t>(v));  // the launcher cleared the dump
+          }
+        }
+      }
       if (!whole) {
-        // split tile: park the partial sums (offset removed), count this CTA in; the last one to arrive adds all
-        // partials in K order and finalizes.  Nobody waits for anybody.
+        // split tile: park the partial sums (offset removed), count this CTA in.  The last CTA to arrive adds all
+        // partials in K order (so the result does not depend on who was last) and does the epilogue.  Nobody waits
+        // for anybody.
         const int t_rel = item.tile - pl.tail_first;
+        const size_t slot_floats = static_cast<size_t>(p.tok_tile) * kBlockCh;
+        float* mine = p.partials + (static_cast<size_t>(cta) * 2 + item.slot) * slot_floats +
+                      static_cast<size_t>(my_col0) * kBlockCh + ch_in_tile;
+#pragma unroll
+        for (int c = 0; c < kCols; c += 2) {
+          const float2 pair = unpack2(sums2[c / 2]);
+          if (c < my_cols) __stcg(mine + c * kBlockCh, __fsub_rn(pair.x, offset_sum));
+          if (c + 1 < my_cols) __stcg(mine + (c + 1) * kBlockCh, __fsub_rn(pair.y, offset_sum));
+        }
         const int total = pl.tail_tiles * groups;
         const int lo_unit = t_rel * groups, hi_unit = lo_unit + groups;
         int c_lo = static_cast<int>((static_cast<long long>(lo_unit) * pl.tail_ctas) / total);
@@ -649,20 +724,10 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         while (c_lo > 0 && unit_start(c_lo, total, pl.tail_ctas) > lo_unit) --c_lo;
         int c_hi = c_lo;
         while (c_hi + 1 < pl.tail_ctas && unit_start(c_hi + 1, total, pl.tail_ctas) < hi_unit) ++c_hi;
-        const size_t slot_floats = static_cast<size_t>(p.tok_tile) * kBlockCh;
-        float* mine = p.partials + (static_cast<size_t>(cta) * 2 + item.slot) * slot_floats;
-        if (my_cols > 0) {
-#pragma unroll
-          for (int c = 0; c < kCols; c += 2) {
-            const float2 pair = unpack2(sums2[c / 2]);
-            if (c < my_cols) __stcg(mine + static_cast<size_t>(my_col0 + c) * kBlockCh + ch_in_tile, __fsub_rn(pair.x, offset_sum));
-            if (c + 1 < my_cols) __stcg(mine + static_cast<size_t>(my_col0 + c + 1) * kBlockCh + ch_in_tile, __fsub_rn(pair.y, offset_sum));
-          }
-        }
         __threadfence();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_meet);
-        if (!mbar_wait_bounded(bar_meet, meets & 1u, abort_flag, kWaitLimitNs)) {
+        if (!wait_on(bar_meet, meets & 1u, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9108);
           ok = false;
           break;
@@ -675,79 +740,37 @@ sq_gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_meet);
-        if (!mbar_wait_bounded(bar_meet, meets & 1u, abort_flag, kWaitLimitNs)) {
+        if (!wait_on(bar_meet, meets & 1u, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9108);
           ok = false;
           break;
         }
         ++meets;
-        finalize = *last_flag != 0;
-        if (finalize) {
+        if (*last_flag != 0) {
           __threadfence();
+          // eight columns at a time: the loads of one contributor are independent of each other
+          for (int c0 = 0; c0 < my_cols; c0 += 8) {
+            float acc[8];
 #pragma unroll
-          for (int i = 0; i < kCols / 2; ++i) sums2[i] = 0ull;
-          offset_sum = 0.0f;
-          for (int c = c_lo; c <= c_hi; ++c) {
-            const int first_tile = unit_start(c, total, pl.tail_ctas) / groups;
-            const int slot = first_tile == t_rel ? 0 : 1;
-            const float* theirs = p.partials + (static_cast<size_t>(c) * 2 + slot) * slot_floats;
-            if (my_cols > 0) {
+            for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+            for (int c = c_lo; c <= c_hi; ++c) {
+              const int first_tile = unit_start(c, total, pl.tail_ctas) / groups;
+              const int slot = first_tile == t_rel ? 0 : 1;
+              const float* theirs = p.partials + (static_cast<size_t>(c) * 2 + slot) * slot_floats +
+                                    static_cast<size_t>(my_col0 + c0) * kBlockCh + ch_in_tile;
+              float part[8];
 #pragma unroll
-              for (int col = 0; col < kCols; col += 2) {
-                float2 pair = unpack2(sums2[col / 2]);
-                if (col < my_cols) pair.x = __fadd_rn(pair.x, __ldcg(theirs + static_cast<size_t>(my_col0 + col) * kBlockCh + ch_in_tile));
-                if (col + 1 < my_cols) pair.y = __fadd_rn(pair.y, __ldcg(theirs + static_cast<size_t>(my_col0 + col + 1) * kBlockCh + ch_in_tile));
-                sums2[col / 2] = pack2(pair.x, pair.y);
-              }
+              for (int j = 0; j < 8; ++j) part[j] = c0 + j < my_cols ? __ldcg(theirs + j * kBlockCh) : 0.0f;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], part[j]);
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (c0 + j < my_cols) emit(acc[j], row_scale[c0 + j], c0 + j);
           }
         }
       }
-
-      const uint32_t rslot = item_idx % kRowScaleSlots, rphase = (item_idx / kRowScaleSlots) & 1u;
-      if (finalize) {
-        if (!mbar_wait_bounded(bar_rs_full + 8 * rslot, rphase, abort_flag, kWaitLimitNs)) {
-          if (lane == 0) report_timeout(p.status, abort_flag, 9109);
-          ok = false;
-          break;
-        }
-        if (n_ok && my_cols > 0) {
-          float wscale = 1.0f;
-          if (!kGroup) wscale = __ldg(static_cast<const float*>(p.w_scales) + n);
-          const bool has_bias = p.bias != nullptr;
-          const float bias = has_bias ? to_float<OutT>(__ldg(static_cast<const OutT*>(p.bias) + n)) : 0.0f;
-          OutT* out = static_cast<OutT*>(p.out) + n;
-          const int64_t m0 = tok0 + my_col0;
-          const uint32_t rs_addr = rs_base + rslot * 512 + static_cast<uint32_t>(my_col0) * 4u;
-#pragma unroll
-          for (int j = 0; j < kCols / 4; ++j) {
-            if (4 * j < my_cols) {
-              float rs[4];
-              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                           : "=f"(rs[0]), "=f"(rs[1]), "=f"(rs[2]), "=f"(rs[3])
-                           : "r"(rs_addr + 16u * j));
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                if (4 * j + e < my_cols) {
-                  const float2 pair = unpack2(sums2[(4 * j + e) / 2]);
-                  const float sum = (e & 1) != 0 ? pair.y : pair.x;
-                  float y;
-                  if (kGroup) y = __fmul_rn(__fsub_rn(sum, offset_sum), __fmul_rn(rs[e], kScaleDown));
-                  else y = __fmul_rn(__fmul_rn(sum, rs[e]), wscale);
-                  if (has_bias) y = __fadd_rn(y, bias);
-                  const int64_t m = m0 + 4 * j + e;
-                  // gate and residual: separate multiply and add, each rounded, as an unfused epilogue would
-                  if (p.gate != nullptr)
-                    y = __fmul_rn(y, to_float<OutT>(__ldg(static_cast<const OutT*>(p.gate) + (m / p.gate_span) * p.gate_row_stride + n)));
-                  if (p.residual != nullptr)
-                    y = __fadd_rn(y, to_float<OutT>(__ldg(static_cast<const OutT*>(p.residual) + m * p.N + n)));
-                  out[m * p.N] = from_float<OutT>(y);
-                }
-              }
-            }
-          }
-        }
-      }
+      if (threadIdx.x == 256) stamp(kTrItemEnd, 8 * item_idx + 7);
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_rs_empty + 8 * rslot);
       ++item_idx;
@@ -989,7 +1012,7 @@ __global__ void __launch_bounds__(128, 1) sq_wait_probe_kernel(uint64_t limit_ns
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&tmem_slot_word);
   if (warp == 1) {
     const uint64_t start = global_timer_ns();
-    const bool arrived = mbar_wait_bounded(bar, 0, abort_flag, limit_ns);
+    const bool arrived = mbar_wait_light(bar, 0, abort_flag, limit_ns);
     if (!arrived && (threadIdx.x & 31) == 0) {
       report_timeout(status, abort_flag, 9190);
       if (waited_ns != nullptr) *waited_ns = static_cast<long long>(global_timer_ns() - start);

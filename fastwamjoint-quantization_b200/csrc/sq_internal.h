@@ -71,7 +71,7 @@ int launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
 int launch_gemm_ts(const GemmArgs& a, cudaStream_t stream);
 int launch_gemm_ts_timeline(const GemmArgs& a, long long* timeline, cudaStream_t stream);
 size_t gemm_split_workspace_bytes(int64_t M);
-// Picks the kernel: the second-generation one unless the weights are prepacked or SQ_GEMM_KERNEL=tc is set.
+// Picks the kernel: sq_gemm_tc.cu unless SQ_GEMM_KERNEL=ts is set (and the weights are not prepacked).
 int launch_gemm(const GemmArgs& a, cudaStream_t stream);
 bool gemm_takes_split_workspace(const GemmArgs& a);
 int launch_gemm_check(const GemmArgs& a, cudaStream_t stream);

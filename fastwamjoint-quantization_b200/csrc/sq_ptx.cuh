@@ -112,6 +112,44 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// The same contract with a lighter loop: the wall clock and the abort flag are looked at once per 256 polls
+// only.  Reading %globaltimer and the flag on every poll made a waiting warp a steady stream of instructions and
+// shared-memory traffic, which slowed the warps doing the work on the same SM several times over.
+__device__ __forceinline__ bool mbar_wait_light(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                uint64_t limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t start = 0;
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;  // the hardware may park the warp for up to 2 us
+    if ((++polls & 255u) == 0u) {
+      if (*abort_flag != 0) return false;
+      const uint64_t now = global_timer_ns();
+      if (start == 0) start = now;
+      else if (now - start > limit_ns) return false;
+    }
+  }
+}
+
+// The same contract on the non-blocking probe: mbarrier.test_wait never parks the warp inside the memory
+// pipeline; between probes the warp sleeps `kSleepNs` in the scheduler (0: pure spin).
+template <int kSleepNs>
+__device__ __forceinline__ bool mbar_wait_probe(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                uint64_t limit_ns) {
+  uint64_t start = 0;
+  uint32_t polls = 0;
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (kSleepNs > 0) asm volatile("nanosleep.u32 %0;" ::"n"(kSleepNs));
+    if ((++polls & 1023u) == 0u) {
+      if (*abort_flag != 0) return false;
+      const uint64_t now = global_timer_ns();
+      if (start == 0) start = now;
+      else if (now - start > limit_ns) return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -122,6 +160,25 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap,
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+
+// 2-D tiled store, shared memory -> global, tracked by the issuing thread's bulk group.  Coordinates are in
+// elements; x * element size must be a multiple of 16 bytes and neither coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, int32_t x, int32_t y, uint32_t src_smem) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(src_smem)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest `kPending` groups of this thread have finished READING shared memory
+template <int kPending>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// ... and have finished writing global memory
+template <int kPending>
+__device__ __forceinline__ void tma_store_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05 / TMEM

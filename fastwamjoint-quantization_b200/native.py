@@ -232,18 +232,18 @@ def linear(x: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, bias, 
 
 
 TIMELINE_ROLES = ("tma_issue", "unpack_start", "unpack_done", "acc_free", "mma_issue", "drain_start",
-                  "acc_released", "drain_done", "mma_committed")
+                  "acc_released", "drain_done", "mma_committed", "drain_top", "acc_loaded", "item_end")
 
 
 def gemm_timeline(codes, packed, w_scales, row_scales, bias):
     """``gemm`` for the group-scale bf16 case plus the pipeline timeline of thread block 0: returns
-    ``(out, stamps)`` with ``stamps`` an int64 [9, 512] tensor of SM clock values (0 = slot not reached);
+    ``(out, stamps)`` with ``stamps`` an int64 [12, 512] tensor of SM clock values (0 = slot not reached);
     rows are named by ``TIMELINE_ROLES``."""
     _require_cuda(codes, "codes")
     m, k = codes.shape
     n = packed.shape[0]
     out = torch.empty((m, n), device=codes.device, dtype=torch.bfloat16)
-    stamps = torch.zeros((9, 512), device=codes.device, dtype=torch.int64)
+    stamps = torch.zeros((len(TIMELINE_ROLES), 512), device=codes.device, dtype=torch.int64)
     with torch.cuda.device(codes.device):
         status = _lib.load_library().sq_gemm_timeline(codes.data_ptr(), packed.data_ptr(), w_scales.data_ptr(),
                                                       row_scales.data_ptr(), _ptr(bias), out.data_ptr(), m, n, k,

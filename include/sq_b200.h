@@ -146,9 +146,11 @@ int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, con
 
 /* Profiling aid with no counterpart in the reference: sq_gemm for the group-scale bf16 case (even-odd codes,
  * M > 128) that also records, for the thread block with index 0, the SM clock at which each pipeline role
- * reached each 128-K block.  `timeline` is int64 [9][512]: rows are TMA issue, unpack start, unpack done,
- * accumulator free, MMA issue, drain start, accumulator released, drain done, MMAs committed; unused slots keep their value. */
-#define SQ_TIMELINE_ROLES 9
+ * reached each 128-K block.  `timeline` is int64 [12][512]: rows are TMA issue, unpack start, unpack done,
+ * accumulator free, MMA issue, drain start, accumulator released, drain done, MMAs committed, top of the drain loop,
+ * accumulator loaded, and (eight slots per work item) the steps of the end-of-item code; unused slots keep their
+ * value.  The first-generation kernel (SQ_GEMM_KERNEL=tc) fills the first nine rows only. */
+#define SQ_TIMELINE_ROLES 12
 #define SQ_TIMELINE_SLOTS 512
 int sq_gemm_timeline(const void* codes, const void* w_packed, const void* w_scales, const float* row_scales,
                      const void* bias, void* out, int64_t M, int64_t N, int64_t K, long long* timeline, void* stream);

@@ -178,7 +178,7 @@ def test_gemm_group_scheme(native, oracle, m, k, n, abits):
         assert torch.equal(acc.cpu().long(), want["acc"])
         assert rel_fro(out.cpu(), want_out) < 1e-2
         # same numbers up to the fp32 summation order of the drain: within one bf16 step almost everywhere
-        assert rel_fro(out.cpu(), want_out) < 2e-3
+        assert rel_fro(out.cpu(), want_out) < 3e-3
         plain = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
                             codes_layout=layout)
         assert torch.equal(plain, out)
