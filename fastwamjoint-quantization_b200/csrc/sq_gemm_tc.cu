@@ -32,6 +32,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 
 #include "sq_internal.h"
@@ -45,10 +46,11 @@ constexpr int kBlockCh = 128;  // output channels per tile = UMMA M = TMEM lanes
 constexpr int kBlockK = 128;   // int8 K elements per stage = one swizzle row = one weight group
 constexpr int kUmmaK = 32;     // K of one kind::i8 instruction
 constexpr int kThreads = 768;  // 4 control + 4 unpack + 16 drain warps
-// Register targets per role after setmaxnreg (control 32, unpack 48, drain 96).  setmaxnreg.inc only hands out
+// Register targets per role after setmaxnreg (control 24, unpack 40, drain 104).  setmaxnreg.inc only hands out
 // registers the CTA was launched with and waits for ever when the targets add up to more, so the launcher
 // checks this sum against (registers per thread at launch) x kThreads before every launch.
-constexpr int kRegisterPoolNeeded = 4 * 32 * 32 + 4 * 32 * 48 + 16 * 32 * 96;
+constexpr int kRegsControl = 32, kRegsUnpack = 48, kRegsDrain = 96;
+constexpr int kRegisterPoolNeeded = 4 * 32 * kRegsControl + 4 * 32 * kRegsUnpack + 16 * 32 * kRegsDrain;
 constexpr uint32_t kPackedBytes = kBlockCh * kBlockK / 2;  // 8 KiB
 constexpr uint32_t kWBytes = kBlockCh * kBlockK;           // 16 KiB
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
@@ -245,7 +247,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 
   if (warp < 4) {
     // ------------------------------------------------------------------ control warpgroup
-    reg_dec<32>();
+    reg_dec<kRegsControl>();
     // Both roles keep the whole warp in the loop and pick the issuing thread with elect.sync: TMA and
     // tcgen05 instructions take warp-uniform operands, and only an elected region lets the compiler keep
     // them in uniform registers (a plain `lane == 0` branch costs about a hundred cycles per instruction).
@@ -359,7 +361,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ converter warpgroup
-    reg_dec<48>();
+    reg_dec<kRegsUnpack>();
     const int ctid = threadIdx.x - 128;  // 0..127
     uint32_t it = 0;
     bool ok = true;
@@ -415,7 +417,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ drain warpgroups
-    reg_inc<96>();
+    reg_inc<kRegsDrain>();
     const int dwarp = warp - 8;           // 0..15
     const int quarter = warp & 3;         // TMEM lane quarter this warp may address
     const int slice = dwarp >> 2;         // which slice of the token columns (four warps per lane quarter)
@@ -444,8 +446,18 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       const int my_cols = min(max(tok_count - my_col0, 0), p.slice_cols);  // real tokens in my slice
       const int64_t n = ch0 + ch_in_tile;
       const bool n_ok = n < p.N;
+      // what the finalize needs from global memory is requested now, a whole tile ahead of its use: lane i keeps the
+      // row scale of column i of this warp's slice (group form: times 2^-49, see kScaleDown), every lane its bias
+      const int64_t m0 = tok0 + my_col0;
+      float my_rs = lane < my_cols ? __ldg(p.row_scales + m0 + lane) : 0.0f;
+      if (kGroup) my_rs = __fmul_rn(my_rs, kScaleDown);
+      const bool has_bias = p.bias != nullptr;
+      const float bias = has_bias && n_ok ? to_float<OutT>(__ldg(static_cast<const OutT*>(p.bias) + n)) : 0.0f;
+      const float wscale = !kGroup && n_ok ? __ldg(static_cast<const float*>(p.w_scales) + n) : 1.0f;
 
-      // group form: packed pairs (columns 2i, 2i + 1); channel form: plain floats
+      // group form: packed pairs (columns 2i, 2i + 1); channel form: plain floats.  (A packed f32x2 FMA issues at
+      // half the rate of a scalar one, so it buys no arithmetic throughput, only fewer instructions: measured 4 %
+      // faster than 32 scalar FFMAs.)
       uint64_t sums2[kGroup ? kCols / 2 : 1];
       float sums[kGroup ? 1 : kCols];
 #pragma unroll
@@ -535,9 +547,9 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           const uint64_t scale2 = pack2(scale, scale);
 #pragma unroll
           for (int i = 0; i < kCols; i += 2) {
-            // group mode: the accumulator is positive and below 2^23, so its bit pattern read as a float is
-            // the denormal acc * 2^-149 and the FFMA takes it as it is (a conversion instruction runs at a
-            // sixteenth of the rate); two columns go through one packed FFMA
+            // group mode: the accumulator is positive and below 2^23, so its bit pattern read as a float is the
+            // denormal acc * 2^-149 and the FFMA takes it as it is (a conversion instruction runs at a sixteenth
+            // of the rate); two columns go through one packed FFMA
             if (kGroup) {
               ffma2(sums2[kGroup ? i / 2 : 0], r[i], r[i + 1], scale2);
             } else {
@@ -562,53 +574,56 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 
       // finalize: row scale, bias, gate, residual, cast, store.  Lanes hold consecutive channels -> 64 B per
       // warp store.  (A version that transposed the block through shared memory to store 16-byte vectors along
-      // the channel axis measured 30 % slower end to end and was dropped.)
-      if (n_ok) {
-        float wscale = 1.0f;
-        if (!kGroup) wscale = __ldg(static_cast<const float*>(p.w_scales) + n);
-        const bool has_bias = p.bias != nullptr;
-        const float bias = has_bias ? to_float<OutT>(__ldg(static_cast<const OutT*>(p.bias) + n)) : 0.0f;
-        OutT* out = static_cast<OutT*>(p.out) + n;
-        const float* rs_ptr = p.row_scales + tok0 + my_col0;
-        const int64_t m0 = tok0 + my_col0;
-        // row scales of four columns at a time, requested one step ahead of their use
-        auto row_scales4 = [&](int j) {
-          float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (4 * j + 4 <= my_cols) {
-            v = __ldg(reinterpret_cast<const float4*>(rs_ptr) + j);
-          } else if (4 * j < my_cols) {
-            v.x = __ldg(rs_ptr + 4 * j);
-            if (4 * j + 1 < my_cols) v.y = __ldg(rs_ptr + 4 * j + 1);
-            if (4 * j + 2 < my_cols) v.z = __ldg(rs_ptr + 4 * j + 2);
+      // the channel axis measured 30 % slower end to end and was dropped.)  The row scale of column i was loaded by
+      // lane i when the tile began and comes over by shuffle, so no global load sits in front of the stores; the
+      // shuffles run in every lane, whether or not its channel exists.
+      const bool plain = p.gate == nullptr && p.residual == nullptr;
+      const bool store_ok = n_ok;
+      OutT* out = static_cast<OutT*>(p.out) + m0 * p.N + (n_ok ? n : 0);
+      if (plain) {
+        // the common case is kept apart from the fused forms: a short straight run of instructions per column
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) {
+          const float rs = __shfl_sync(0xffffffffu, my_rs, i);
+          float y;
+          if (kGroup) {
+            const float2 pair = unpack2(sums2[kGroup ? i / 2 : 0]);
+            y = __fmul_rn(__fsub_rn((i & 1) != 0 ? pair.y : pair.x, offset_sum), rs);
+          } else {
+            y = __fmul_rn(__fmul_rn(sums[kGroup ? 0 : i], rs), wscale);
           }
-          return v;
-        };
-        // (group form only: in the channel form the extra live registers cost more than the latency saved)
-        float4 ahead = kGroup ? row_scales4(0) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (has_bias) y = __fadd_rn(y, bias);
+          if (store_ok && i < my_cols) *out = from_float<OutT>(y);
+          out += p.N;
+        }
+      } else {
+        // gate rows change every gate_span tokens: one division for the first column, then a running remainder
+        int64_t gate_row = m0 / p.gate_span;
+        int64_t gate_left = p.gate_span - m0 % p.gate_span;  // columns before the next gate row
+        const OutT* gate = p.gate != nullptr ? static_cast<const OutT*>(p.gate) + gate_row * p.gate_row_stride + (n_ok ? n : 0) : nullptr;
+        const OutT* residual = p.residual != nullptr ? static_cast<const OutT*>(p.residual) + m0 * p.N + (n_ok ? n : 0) : nullptr;
 #pragma unroll
-        for (int j = 0; j < kCols / 4; ++j) {
-          const float4 current = kGroup ? ahead : row_scales4(j);
-          if (kGroup && j + 1 < kCols / 4) ahead = row_scales4(j + 1);
-          if (4 * j < my_cols) {
-            const float rs[4] = {current.x, current.y, current.z, current.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (4 * j + e < my_cols) {
-                float y;
-                if (kGroup) {
-                  const float2 pair = unpack2(sums2[kGroup ? (4 * j + e) / 2 : 0]);
-                  y = __fmul_rn(__fsub_rn((e & 1) != 0 ? pair.y : pair.x, offset_sum), __fmul_rn(rs[e], kScaleDown));
-                } else {
-                  y = __fmul_rn(__fmul_rn(sums[kGroup ? 0 : 4 * j + e], rs[e]), wscale);
-                }
-                if (has_bias) y = __fadd_rn(y, bias);
-                const int64_t m = m0 + 4 * j + e;
-                if (p.gate != nullptr)
-                  y *= to_float<OutT>(__ldg(static_cast<const OutT*>(p.gate) + (m / p.gate_span) * p.gate_row_stride + n));
-                if (p.residual != nullptr) y += to_float<OutT>(__ldg(static_cast<const OutT*>(p.residual) + m * p.N + n));
-                out[m * p.N] = from_float<OutT>(y);
-              }
-            }
+        for (int i = 0; i < kCols; ++i) {
+          const float rs = __shfl_sync(0xffffffffu, my_rs, i);
+          float y;
+          if (kGroup) {
+            const float2 pair = unpack2(sums2[kGroup ? i / 2 : 0]);
+            y = __fmul_rn(__fsub_rn((i & 1) != 0 ? pair.y : pair.x, offset_sum), rs);
+          } else {
+            y = __fmul_rn(__fmul_rn(sums[kGroup ? 0 : i], rs), wscale);
+          }
+          if (has_bias) y = __fadd_rn(y, bias);
+          if (store_ok && i < my_cols) {
+            // gate and residual: a separate multiply and add, each rounded, as an unfused epilogue would
+            if (gate != nullptr) y = __fmul_rn(y, to_float<OutT>(__ldg(gate)));
+            if (residual != nullptr) y = __fadd_rn(y, to_float<OutT>(__ldg(residual)));
+            *out = from_float<OutT>(y);
+          }
+          out += p.N;
+          if (residual != nullptr) residual += p.N;
+          if (gate != nullptr && --gate_left == 0) {
+            gate_left = p.gate_span;
+            gate += p.gate_row_stride;
           }
         }
       }

@@ -101,15 +101,20 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 // Wait for `parity` of barrier `bar`.  Returns false when the wait gave up: either
 // `*abort_flag` (shared memory, set by any role that timed out) became non-zero or
 // `limit_ns` of wall-clock passed.  On a timeout the caller records the status.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint64_t limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
+// The polling loop is a function of its own, not inlined: a kernel has a dozen waits inside its inner loops, and the
+// instruction cache holds those loops only while they stay short.
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns) {
   const uint64_t start = global_timer_ns();
   while (true) {
     if (mbar_try_wait_hint(bar, parity, 20000u)) return true;  // up to 20 us asleep per poll
     if (*abort_flag != 0) return false;
     if (global_timer_ns() - start > limit_ns) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint64_t limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, limit_ns);
 }
 
 // The same contract with a lighter loop: the wall clock and the abort flag are looked at once per 256 polls

@@ -92,6 +92,28 @@ class TokenQuantLinear(nn.Module):
             y = F.gelu(y)
         return y if residual is None else residual + y
 
+    @torch.no_grad()
+    def input_codes(self, x: torch.Tensor, *, rms_eps: float | None = None, input_activation: str | None = None,
+                    backend: str = "native") -> torch.Tensor:
+        """The integer activation codes this linear computes for input ``x`` (natural k order), for parity
+        diagnostics: the optional GELU / RMSNorm in front are done in torch and rounded to x's dtype for both
+        backends, so what is compared is the rotation and the quantizer."""
+        if input_activation == "gelu":
+            x = F.gelu(x)
+        if rms_eps is not None:
+            x = rms_norm(x, rms_eps)
+        if backend == "native":
+            codes, _ = native.prepass(x, abits=self.activation_bits, mode="token", signs=self.input_rotation_signs,
+                                      codes_layout=native._lib.CODES_NATURAL)
+            return codes.reshape(*x.shape[:-1], self.in_features)
+        values = x.float()
+        if self.input_rotation_signs is not None:
+            values = randomized_block_hadamard_transform(values, self.input_rotation_signs, 128).to(x.dtype).float()
+        qmax = (1 << (self.activation_bits - 1)) - 1
+        amax = values.abs().amax(dim=-1, keepdim=True)
+        scale = (amax / torch.full_like(amax, float(qmax))).clamp_min(1e-8)
+        return (values / scale).round().clamp(-qmax, qmax).to(torch.int8)
+
     def _reference_linear(self, x: torch.Tensor) -> torch.Tensor:
         values = x.float()
         if self.input_rotation_signs is not None:
@@ -200,3 +222,59 @@ class SyntheticDiT(nn.Module):
             (velocity,) = self._joint_denoise_core(x)
             x = x - velocity / num_inference_steps
         return x
+
+
+def _rel_fro(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30))
+
+
+@torch.no_grad()
+def stack_parity(model: SyntheticDiT, tokens: torch.Tensor) -> dict:
+    """How far the native stack is from its fake-quant reference backend, layer by layer and block by block.
+
+    ``linear``          every linear gets the REFERENCE stack's input of that linear on both backends: relative
+                        Frobenius error of its output (largest of the block's four).  This is the kernels' own
+                        error, the quantity the 1e-2 output tolerance is about.
+    ``code_mismatch``   on the same inputs, the largest fraction of activation codes that differ.
+    ``teacher_forced``  every block gets the reference stack's input of that block on both backends: error of the
+                        block output.  Inside a block the four linears already feed each other, so this includes
+                        how one block of the (random, untrained) stack amplifies a flipped activation code.
+    ``free_running``    both stacks run from ``tokens`` on their own: error of the native activations after each block.
+    ``output``          the summary, errors after the final norm included.  The reference backend's dequantized
+                        weights are freed block by block, so the extra memory is one block's worth."""
+    report = {"linear": [], "code_mismatch": [], "teacher_forced": [], "free_running": []}
+    reference_x = native_x = tokens
+    for block in model.blocks:
+        captured = []
+        layers = [m for m in block.modules() if isinstance(m, TokenQuantLinear)]
+        hooks = [layer.register_forward_pre_hook(lambda mod, args, kwargs: captured.append((mod, args[0], dict(kwargs))),
+                                                 with_kwargs=True) for layer in layers]
+        for layer in layers:
+            layer.backend = "reference"
+        reference_out = block(reference_x)
+        for hook in hooks:
+            hook.remove()
+        worst_codes = worst_linear = 0.0
+        for layer, x_in, kwargs in captured:
+            front = {key: kwargs.get(key) for key in ("rms_eps", "input_activation")}
+            ours = layer.input_codes(x_in, backend="native", **front)
+            theirs = layer.input_codes(x_in, backend="reference", **front)
+            worst_codes = max(worst_codes, float((ours != theirs).float().mean()))
+            want = layer(x_in, **kwargs)
+            layer.backend = "native"
+            worst_linear = max(worst_linear, _rel_fro(layer(x_in, **kwargs), want))
+            layer.backend = "reference"
+        for layer in layers:
+            layer.backend = "native"
+            layer._dequantized = None
+        report["linear"].append(worst_linear)
+        report["code_mismatch"].append(worst_codes)
+        report["teacher_forced"].append(_rel_fro(block(reference_x), reference_out))
+        native_x = block(native_x)
+        report["free_running"].append(_rel_fro(native_x, reference_out))
+        reference_x = reference_out
+    eps = model.config.eps
+    report["output"] = {"linear_max": max(report["linear"]), "code_mismatch_max": max(report["code_mismatch"]),
+                        "teacher_forced_max": max(report["teacher_forced"]),
+                        "free_running": _rel_fro(rms_norm(native_x, eps), rms_norm(reference_x, eps))}
+    return report

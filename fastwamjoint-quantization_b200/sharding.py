@@ -3,9 +3,10 @@
 * Token (M) sharding - the primary form: weights replicated, rank r owns rows ``[r*M/G, (r+1)*M/G)``; rows are
   independent through pre-pass, GEMM and epilogue, so the data path has no collective at all.
 * Output-channel (N) split of one wide layer: rank r owns ``W[r*N/G:(r+1)*N/G]`` and computes ``[M, N/G]``;
-  the slices are all-gathered (NCCL over NVLink on GPUs, gloo in CPU tests) and laid side by side.  The
-  gather moves ``2*M*N*(G-1)/G`` bytes per rank and is communication-bound for every shape of interest; it
-  exists because the benchmark configuration names it.  Plain NCCL all-gather, no peer-memory kernels.
+  the slices are all-gathered (NCCL over NVLink on GPUs, gloo in CPU tests) and laid side by side, optionally in
+  token chunks so the gather of one chunk overlaps the GEMM of the next.  The gather moves ``2*M*N*(G-1)/G``
+  bytes into every rank and is communication-bound for every shape of interest; it exists because the benchmark
+  configuration names it.  Plain NCCL all-gather, no peer-memory kernels.
 
 The host-side logic (row ranges, slice ownership, gather + re-layout) is device independent and is tested
 with world-size-2 gloo process groups on CPU with a stand-in for the local linear.
@@ -35,20 +36,44 @@ def channel_range(channels: int, rank: int, world: int, multiple: int = 8) -> tu
     return rank * width, (rank + 1) * width
 
 
-def token_sharded_linear(x_local: torch.Tensor, linear: Callable[[torch.Tensor], torch.Tensor]) -> torch.Tensor:
-    """Rank-local rows in, rank-local rows out: no communication."""
-    return linear(x_local)
-
-
 def channel_split_linear(x: torch.Tensor, linear_slice: Callable[[torch.Tensor], torch.Tensor], *,
-                         group=None) -> torch.Tensor:
+                         group=None, chunks: int = 1) -> torch.Tensor:
     """Every rank holds the full ``x`` and a slice of the weight; returns the full ``[..., N]`` output on every
-    rank: local GEMM, all-gather of the ``[..., N/G]`` slices, concatenation along the channel axis."""
-    part = linear_slice(x).contiguous()
+    rank: local GEMM, all-gather of the ``[..., N/G]`` slices, concatenation along the channel axis.
+
+    ``chunks > 1`` cuts the token rows into that many pieces and overlaps communication with compute on CUDA
+    devices: the GEMM of piece i + 1 runs on the current stream while the all-gather and the re-layout of piece i
+    run on a side stream (NCCL's own kernels; nothing here touches peer memory).  On the CPU (gloo) the pieces
+    simply run one after the other, which exercises the same slicing."""
     world = dist.get_world_size(group)
-    flat = part.reshape(-1, part.shape[-1])
-    gathered = torch.empty((world * flat.shape[0], flat.shape[1]), dtype=part.dtype, device=part.device)
-    dist.all_gather_into_tensor(gathered, flat, group=group)  # rank-major concatenation of the slices
-    # [G, rows, N/G] -> [rows, G, N/G] -> [..., N]
-    wide = gathered.reshape(world, flat.shape[0], flat.shape[1]).transpose(0, 1)
-    return wide.reshape(*part.shape[:-1], world * part.shape[-1])
+    rows_shape = x.shape[:-1]
+    flat_x = x.reshape(-1, x.shape[-1])
+    rows = flat_x.shape[0]
+    chunks = max(1, min(int(chunks), rows))
+    bounds = [row_range(rows, i, chunks) for i in range(chunks)]
+    on_gpu = x.is_cuda
+    side = torch.cuda.Stream(device=x.device) if on_gpu and chunks > 1 else None
+    out = None
+    for lo, hi in bounds:
+        part = linear_slice(flat_x[lo:hi]).contiguous()
+        width = part.shape[-1]
+        if out is None:
+            out = torch.empty((rows, world * width), dtype=part.dtype, device=part.device)
+        gathered = torch.empty((world, hi - lo, width), dtype=part.dtype, device=part.device)
+
+        def gather_and_place(part=part, gathered=gathered, lo=lo, hi=hi, width=width):
+            dist.all_gather_into_tensor(gathered.view(world * (hi - lo), width), part, group=group)
+            # [G, rows, N/G] -> [rows, G, N/G]: rank r's channels land at columns [r*N/G, (r+1)*N/G)
+            out[lo:hi].view(hi - lo, world, width).copy_(gathered.transpose(0, 1))
+
+        if side is None:
+            gather_and_place()
+        else:
+            side.wait_stream(torch.cuda.current_stream(x.device))  # the piece's GEMM has been queued: wait for it
+            with torch.cuda.stream(side):
+                gather_and_place()
+            for tensor in (part, gathered, out):
+                tensor.record_stream(side)
+    if side is not None:
+        torch.cuda.current_stream(x.device).wait_stream(side)
+    return out.reshape(*rows_shape, out.shape[-1])

@@ -25,17 +25,21 @@ def _worker(rank, world, port, results):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         gen = torch.Generator().manual_seed(0)
-        x = torch.randn(10, 16, generator=gen)
-        w = torch.randn(24, 16, generator=gen)
+        # small integers: every product and sum is exact, whatever the row count of a matmul call
+        x = torch.randint(-4, 5, (10, 16), generator=gen).float()
+        w = torch.randint(-4, 5, (24, 16), generator=gen).float()
         full = x @ w.t()
         # tokens sharded, weights replicated: no communication, ranks' rows tile the full result
         lo, hi = sharding.row_range(10, rank, world)
-        local = sharding.token_sharded_linear(x[lo:hi], lambda t: t @ w.t())
+        local = x[lo:hi] @ w.t()  # rank-local rows in, rank-local rows out: nothing to call
         ok_rows = torch.equal(local, full[lo:hi])
         # channels split, all-gather
         c0, c1 = sharding.channel_range(24, rank, world, multiple=4)
         gathered = sharding.channel_split_linear(x, lambda t: t @ w[c0:c1].t())
         ok_cols = torch.equal(gathered, full)
+        for chunks in (2, 3, 64):  # token chunks (the form that overlaps gather and GEMM on GPUs), ragged and over-split
+            piecewise = sharding.channel_split_linear(x.reshape(2, 5, 16), lambda t: t @ w[c0:c1].t(), chunks=chunks)
+            ok_cols = ok_cols and torch.equal(piecewise, full.reshape(2, 5, 24))
         results[rank] = (ok_rows, ok_cols, (lo, hi), (c0, c1))
     finally:
         dist.destroy_process_group()
