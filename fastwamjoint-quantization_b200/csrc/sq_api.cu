@@ -497,6 +497,7 @@ const char* sq_status_string(int status) {
     case SQ_ERR_DEVICE_WAIT: return "a kernel gave up a bounded wait";
     case SQ_ERR_SCRATCH_LIMIT: return "rows * K is beyond the library-owned scratch of sq_linear_noalloc";
     case 9006: return "device: the MMA rate probe timed out waiting for its MMAs";
+    case 9007: return "device: drain warp timed out waiting for its partner at a block of group scales";
     case 9101: return "device: TMA producer timed out waiting for a free stage";
     case 9102: return "device: MMA warp timed out waiting for a free accumulator";
     case 9103: return "device: MMA warp timed out waiting for operands";

@@ -58,7 +58,7 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 // Timeline capture (debug entry point sq_gemm_timeline): CTA 0 stamps clock64() per K block.
 constexpr int kTraceSlots = 512;
 enum TraceRole { kTrTmaIssue = 0, kTrConvStart, kTrConvDone, kTrMmaAccFree, kTrMmaIssue, kTrDrainStart,
-                 kTrDrainRelease, kTrDrainDone, kTrMmaCommitted, kTraceRoles };
+                 kTrDrainRelease, kTrDrainDone, kTrMmaCommitted, kTrIssuerWaits, kTrDrainWaits, kTrTileEnds, kTraceRoles };
 
 // Group mode keeps every accumulator positive: before the real MMAs of a group, MMAs of a constant tile (both
 // operands the same bytes c) put 32 c^2 per MMA into each element.  A positive int32 below 2^23 read as a float
@@ -75,9 +75,15 @@ constexpr float kScaleDown = 562949953421312.0f;     // 2^49 = 2^149 / 2^96 / 16
 constexpr int kNumConverterWarps = 4;
 constexpr int kNumDrainWarps = 16;  // four per TMEM lane quarter, each owns a slice of the token columns
 
+#ifndef SQ_TC_STAGES128
+#define SQ_TC_STAGES128 5
+#endif
+#ifndef SQ_TC_EARLY_PROBE
+#define SQ_TC_EARLY_PROBE 1
+#endif
 __host__ __device__ constexpr int stages_for(int tok) {
   // shared memory per stage: unpacked weights + codes + packed weights
-  return tok == 128 ? 5 : tok == 64 ? 6 : 7;
+  return tok == 128 ? SQ_TC_STAGES128 : tok == 64 ? 6 : 7;
 }
 __host__ __device__ constexpr uint32_t stage_bytes(int tok) { return kWBytes + tok * kBlockK + kPackedBytes; }
 __host__ __device__ constexpr uint32_t smem_bytes_for(int tok) {
@@ -311,12 +317,13 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           // channel form: tile parity picks the buffer pair, the issuer its half of it
           const uint32_t buf = kGroup ? git % kAccBufs : (git & 1u) * 2u + mine;
           const uint32_t aphase = kGroup ? (git / kAccBufs) & 1u : (git >> 1) & 1u;
+          if (lane == 0) stamp(kTrIssuerWaits, git);
           if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9002);
             ok = false;
             break;
           }
-          if (warp == 1 && lane == 0) stamp(kTrMmaAccFree, git);
+          if (lane == 0) stamp(kTrMmaAccFree, git);
           const uint32_t tmem_d = tmem_base + buf * kBufStride;
           if (kGroup) {
             // the offset MMAs need no operand from the pipeline: they start the accumulator at a positive value
@@ -338,7 +345,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               break;
             }
             tc_fence_after_sync();
-            if (warp == 1 && lane == 0) stamp(kTrMmaIssue, it);
+            if (lane == 0) stamp(kTrMmaIssue, it);
             if (elect_one()) {
               const uint64_t desc_a = umma_desc_k128(w_ring + s * kWBytes);
               const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
@@ -355,7 +362,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             }
             __syncwarp();
           }
-          if (warp == 1 && lane == 0) stamp(kTrMmaCommitted, git);
+          if (lane == 0) stamp(kTrMmaCommitted, git);
         }
       }
     }
@@ -365,10 +372,11 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     const int ctid = threadIdx.x - 128;  // 0..127
     uint32_t it = 0;
     bool ok = true;
+    bool stage_ready = false;  // an early probe saw the coming stage's packed weights landed
     for (int tile = blockIdx.x; !kPre && tile < num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
         const uint32_t s = it % S, phase = (it / S) & 1u;
-        if (!mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs)) {
+        if (!(SQ_TC_EARLY_PROBE && stage_ready) && !mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9004);
           ok = false;
           break;
@@ -385,6 +393,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
                        : "=r"(win[u4][0]), "=r"(win[u4][1]), "=r"(win[u4][2]), "=r"(win[u4][3])
                        : "r"(src + unit * 16));
         }
+        // the next stage's barrier is probed under this stage's work (a probe takes over a hundred cycles)
+        if (SQ_TC_EARLY_PROBE) stage_ready = mbar_test_wait(bar_full + 8 * ((it + 1) % S), (((it + 1) / S) & 1u));
 #pragma unroll
         for (int u4 = 0; u4 < 4; ++u4) {
           const int unit = u4 * 128 + ctid;
@@ -438,6 +448,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 
     uint32_t git = 0;
     bool ok = true;
+    bool acc_ready = false;  // an early probe saw the coming group's accumulator complete
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int ch0 = (tile % p.ch_tiles) * kBlockCh;
       const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
@@ -488,6 +499,42 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const uint32_t aphase = kGroup ? (git / kAccBufs) & 1u : (git >> 1) & 1u;
         const bool split = !kGroup && p.mma_split == 2;
         float scale = 0.0625f;  // the unpacked weights are 16 x the int4 value
+        if (threadIdx.x == 256) stamp(kTrDrainWaits, git);
+        // (group form: usually the probe made during the previous group already saw this barrier complete)
+        if (!(kGroup && SQ_TC_EARLY_PROBE && acc_ready) &&
+            !mbar_wait_bounded(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
+          if (lane == 0) report_timeout(p.status, abort_flag, 9005);
+          ok = false;
+          break;
+        }
+        if (split && !mbar_wait_bounded(bar_acc_full + 8 * (buf + 1), aphase, abort_flag, kWaitLimitNs)) {
+          if (lane == 0) report_timeout(p.status, abort_flag, 9005);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        if (threadIdx.x == 256) stamp(kTrDrainStart, git);
+        uint32_t r[kCols];
+        const uint32_t taddr = tmem_base + lane_addr + buf * kBufStride + my_col0;
+        if (my_cols > 0) {
+          tmem_ld_chunk(taddr, r);
+          if (!kGroup) {
+            if (split) {
+              uint32_t other[kCols];
+              tmem_ld_chunk(taddr + kBufStride, other);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < kCols; ++i) r[i] += other[i];  // exact: int32 partial sums of disjoint K blocks
+            } else {
+              tmem_wait_ld();
+            }
+          }
+        }
+        // A probe of an mbarrier takes over a hundred cycles to answer even when the phase is long complete: the
+        // next group's barrier is probed now, under the load, instead of in front of the next load.
+        if (kGroup && SQ_TC_EARLY_PROBE)
+          acc_ready = mbar_test_wait(bar_acc_full + 8 * ((git + 1) % kAccBufs), ((git + 1) / kAccBufs) & 1u);
+        // the scale of this group is picked while the load is in flight
         if (kGroup) {
           unsigned short raw;
           if (scale_vectors) {
@@ -509,32 +556,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           scale = __half2float(__ushort_as_half(raw)) * kScaleUp;
           offset_sum = fmaf(offset_float, scale, offset_sum);
         }
-        if (!mbar_wait_bounded(bar_acc_full + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
-          if (lane == 0) report_timeout(p.status, abort_flag, 9005);
-          ok = false;
-          break;
-        }
-        if (split && !mbar_wait_bounded(bar_acc_full + 8 * (buf + 1), aphase, abort_flag, kWaitLimitNs)) {
-          if (lane == 0) report_timeout(p.status, abort_flag, 9005);
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        if (threadIdx.x == 256) stamp(kTrDrainStart, git);
-        uint32_t r[kCols];
-        const uint32_t taddr = tmem_base + lane_addr + buf * kBufStride + my_col0;
-        if (my_cols > 0) {
-          tmem_ld_chunk(taddr, r);
-          if (split) {
-            uint32_t other[kCols];
-            tmem_ld_chunk(taddr + kBufStride, other);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < kCols; ++i) r[i] += other[i];  // exact: int32 partial sums of disjoint K blocks
-          } else {
-            tmem_wait_ld();
-          }
-        }
+        if (kGroup && my_cols > 0) tmem_wait_ld();
         // the accumulator is in registers: give it back before doing the arithmetic
         tc_fence_before_sync();
         __syncwarp();
@@ -580,6 +602,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       const bool plain = p.gate == nullptr && p.residual == nullptr;
       const bool store_ok = n_ok;
       OutT* out = static_cast<OutT*>(p.out) + m0 * p.N + (n_ok ? n : 0);
+      if (threadIdx.x == 256) stamp(kTrTileEnds, 2 * (git / groups) - 2);  // finalize begins / has ended
       if (plain) {
         // the common case is kept apart from the fused forms: a short straight run of instructions per column
 #pragma unroll
@@ -627,6 +650,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           }
         }
       }
+      if (threadIdx.x == 256) stamp(kTrTileEnds, 2 * (git / groups) - 1);
     }
   }
 
