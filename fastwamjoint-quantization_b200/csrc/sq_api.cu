@@ -69,7 +69,7 @@ static bool second_generation_requested() {
   return requested;
 }
 
-bool gemm_takes_split_workspace(const GemmArgs& a) { return !a.weights_prepacked && second_generation_requested(); }
+bool gemm_takes_split_workspace(const GemmArgs&) { return true; }  // both kernels split K when tiles are few
 
 int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (a.weights_prepacked || !second_generation_requested()) return launch_gemm_tc(a, stream);

@@ -103,6 +103,12 @@ struct TcParams {
   int tok_tile;   // tokens per tile at run time: a multiple of 16, <= TOK
   int slice_cols;  // token columns per drain warp: drain warp j of a lane quarter owns [j, j + 1) * slice_cols
   int mma_split;        // channel form: 2 when both issuers have K blocks to take (k_blocks >= 2), else 1
+  // K split (few tiles, many K blocks): a work item is one of `splits` parts of a tile's K blocks; every part leaves
+  // its sums in `partials` ([item][token column][128 channels], fp32 or int32 bits) and the part whose drain warp
+  // arrives last at the tile's counter (one 4-bit field per drain warp) adds them in part order and finalizes
+  int splits;
+  float* partials;
+  unsigned long long* counters;
   int offset_steps;     // group mode: constant-tile MMAs in front of every group (1 or 4)
   uint32_t offset_word;  // four copies of the constant tile's byte
   uint32_t offset_bits;  // what those MMAs add to every accumulator element
@@ -244,12 +250,28 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int num_tiles = p.ch_tiles * p.tok_tiles;
+  // K is split only by the small-tile kernels (few tokens: few tiles); the 128-token kernel carries none of that code
+  constexpr bool kSplitK = TOK <= 64;
+  const int splits = kSplitK ? p.splits : 1;
+  const int num_items = num_tiles * splits;
+  // a work item is a tile, or one part of a tile's K blocks: [kb0, kb1)
+  auto item_range = [&](int item, int& tile, int& kb0, int& kb1) {
+    if (kSplitK) {
+      tile = item / splits;
+      const int part = item - tile * splits;
+      kb0 = static_cast<int>(static_cast<int64_t>(part) * p.k_blocks / splits);
+      kb1 = static_cast<int>(static_cast<int64_t>(part + 1) * p.k_blocks / splits);
+    } else {
+      tile = item;
+      kb0 = 0;
+      kb1 = p.k_blocks;
+    }
+  };
   const bool tracing = kTrace && blockIdx.x == 0 && p.timeline != nullptr;
   auto stamp = [&](int role, uint32_t slot) {
     if (kTrace && tracing && slot < kTraceSlots) p.timeline[role * kTraceSlots + slot] = clock64();
   };
-  const int groups = kGroup ? p.k_blocks : 1;
-  const int blocks_per_group = kGroup ? 1 : p.k_blocks;
+  const int groups = kGroup ? p.k_blocks : 1;  // of a whole tile: what scale rows and accumulator dumps are indexed by
 
   if (warp < 4) {
     // ------------------------------------------------------------------ control warpgroup
@@ -261,10 +283,12 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       // TMA producer
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        int tile, kb0, kb1;
+        item_range(item, tile, kb0, kb1);
         const int ch0 = (tile % p.ch_tiles) * kBlockCh;
         const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % S, phase = (it / S) & 1u;
           if (!mbar_wait_bounded(bar_empty + 8 * s, phase ^ 1u, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9001);
@@ -298,7 +322,11 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       const uint32_t mine = static_cast<uint32_t>(warp - 1);
       uint32_t it = 0, git = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        int tile, kb0, kb1;
+        item_range(item, tile, kb0, kb1);
+        const int groups = kGroup ? kb1 - kb0 : 1;
+        const int blocks_per_group = kGroup ? 1 : kb1 - kb0;
         const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
         const int64_t left = p.M - tok0;
         const int tok_count = left < p.tok_tile ? static_cast<int>(left) : p.tok_tile;
@@ -309,7 +337,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             it += blocks_per_group;
             continue;
           }
-          const uint32_t split = kGroup ? 1u : static_cast<uint32_t>(p.mma_split);
+          const uint32_t split = (kGroup || blocks_per_group < 2) ? 1u : static_cast<uint32_t>(p.mma_split);
           if (!kGroup && mine >= split) {
             it += blocks_per_group;
             continue;
@@ -373,8 +401,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     uint32_t it = 0;
     bool ok = true;
     bool stage_ready = false;  // an early probe saw the coming stage's packed weights landed
-    for (int tile = blockIdx.x; !kPre && tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+    for (int item = blockIdx.x; !kPre && item < num_items && ok; item += gridDim.x) {
+      int tile, kb0, kb1;
+      item_range(item, tile, kb0, kb1);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const uint32_t s = it % S, phase = (it / S) & 1u;
         if (!(SQ_TC_EARLY_PROBE && stage_ready) && !mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9004);
@@ -449,7 +479,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     uint32_t git = 0;
     bool ok = true;
     bool acc_ready = false;  // an early probe saw the coming group's accumulator complete
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      int tile, kb0, kb1;
+      item_range(item, tile, kb0, kb1);
+      const int g0 = kGroup ? kb0 : 0, g1 = kGroup ? kb1 : 1;  // this item's groups
       const int ch0 = (tile % p.ch_tiles) * kBlockCh;
       const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
       const int64_t left = p.M - tok0;
@@ -460,6 +493,9 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       // what the finalize needs from global memory is requested now, a whole tile ahead of its use: lane i keeps the
       // row scale of column i of this warp's slice (group form: times 2^-49, see kScaleDown), every lane its bias
       const int64_t m0 = tok0 + my_col0;
+      float* part_out = kSplitK && splits > 1
+                            ? p.partials + (static_cast<int64_t>(item) * p.tok_tile + my_col0) * kBlockCh + ch_in_tile
+                            : nullptr;
       float my_rs = lane < my_cols ? __ldg(p.row_scales + m0 + lane) : 0.0f;
       if (kGroup) my_rs = __fmul_rn(my_rs, kScaleDown);
       const bool has_bias = p.bias != nullptr;
@@ -485,19 +521,22 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       unsigned short raw_a = 0, raw_b = 0;
       if (kGroup) {
         if (scale_vectors) {
-          chunk = __ldg(reinterpret_cast<const uint4*>(my_scales));
-          if (groups > 8) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + 1);
+          chunk = __ldg(reinterpret_cast<const uint4*>(my_scales) + (g0 >> 3));
+          if (8 * ((g0 >> 3) + 1) < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + (g0 >> 3) + 1);
         } else {
-          raw_a = __ldg(my_scales);
-          if (groups > 1) raw_b = __ldg(my_scales + 1);
+          // raw_a holds the scale of the next even group, raw_b of the next odd one
+          const unsigned short first = __ldg(my_scales + g0);
+          const unsigned short second = g0 + 1 < groups ? __ldg(my_scales + g0 + 1) : static_cast<unsigned short>(0);
+          raw_a = (g0 & 1) == 0 ? first : second;
+          raw_b = (g0 & 1) == 0 ? second : first;
         }
       }
 
-      for (int g = 0; g < groups && ok; ++g, ++git) {
+      for (int g = g0; g < g1 && ok; ++g, ++git) {
         // channel form: the tile's accumulator pair (2j, 2j + 1), the second in use when the issuers split K
         const uint32_t buf = kGroup ? git % kAccBufs : (git & 1u) * 2u;
         const uint32_t aphase = kGroup ? (git / kAccBufs) & 1u : (git >> 1) & 1u;
-        const bool split = !kGroup && p.mma_split == 2;
+        const bool split = !kGroup && p.mma_split == 2 && kb1 - kb0 >= 2;
         float scale = 0.0625f;  // the unpacked weights are 16 x the int4 value
         if (threadIdx.x == 256) stamp(kTrDrainWaits, git);
         // (group form: usually the probe made during the previous group already saw this barrier complete)
@@ -589,10 +628,83 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               }
             }
           }
+          if (kSplitK && !kGroup && splits > 1) {
+            // channel form under a K split: the parts exchange the exact int32 accumulators
+#pragma unroll
+            for (int i = 0; i < kCols; ++i)
+              if (i < my_cols) part_out[i * kBlockCh] = __uint_as_float(r[i]);
+          }
         }
         if (threadIdx.x == 256) stamp(kTrDrainDone, git);
       }
       if (!ok) break;
+
+      if (kSplitK && splits > 1) {
+        // K split: leave this part's sums, take a ticket at the tile's counter; the last of the `splits` parts adds
+        // all of them in part order (so the result does not depend on which part came last) and goes on to finalize.
+        // Nobody waits for anybody.  Warps without columns of this tile (my_cols == 0) have nothing to do in any part.
+        if (my_cols == 0) continue;
+        if (kGroup) {
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) {
+            const float2 pair = unpack2(sums2[kGroup ? i / 2 : 0]);
+            if (i < my_cols) part_out[i * kBlockCh] = __fsub_rn((i & 1) != 0 ? pair.y : pair.x, offset_sum);
+          }
+        }
+        __threadfence();
+        __syncwarp();
+        unsigned long long before = 0ull;
+        if (lane == 0) before = atomicAdd(p.counters + tile, 1ull << (4 * dwarp));
+        before = __shfl_sync(0xffffffffu, before, 0);
+        if (static_cast<int>((before >> (4 * dwarp)) & 15ull) != splits - 1) continue;  // another part finalizes
+        __threadfence();
+        if (lane == 0) atomicAdd(p.counters + tile, ~(static_cast<unsigned long long>(splits) << (4 * dwarp)) + 1ull);
+        const float* part_in = p.partials + (static_cast<int64_t>(tile) * splits * p.tok_tile + my_col0) * kBlockCh + ch_in_tile;
+        if (kGroup) {
+          // the loads of the next part are in flight while this part is added (parts are added in part order)
+          float total[kCols], ahead[kCols];
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) {
+            total[i] = 0.0f;
+            ahead[i] = i < my_cols ? __ldcg(part_in + static_cast<int64_t>(i) * kBlockCh) : 0.0f;
+          }
+          for (int part = 0; part < splits; ++part) {
+            float now[kCols];
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) {
+              now[i] = ahead[i];
+              if (part + 1 < splits && i < my_cols)
+                ahead[i] = __ldcg(part_in + (static_cast<int64_t>(part + 1) * p.tok_tile + i) * kBlockCh);
+            }
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) total[i] = __fadd_rn(total[i], now[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < kCols; i += 2) sums2[kGroup ? i / 2 : 0] = pack2(total[i], total[i + 1]);
+          offset_sum = 0.0f;
+        } else {
+          int32_t total[kCols];
+          float ahead[kCols];
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) {
+            total[i] = 0;
+            ahead[i] = i < my_cols ? __ldcg(part_in + static_cast<int64_t>(i) * kBlockCh) : 0.0f;
+          }
+          for (int part = 0; part < splits; ++part) {
+            float now[kCols];
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) {
+              now[i] = ahead[i];
+              if (part + 1 < splits && i < my_cols)
+                ahead[i] = __ldcg(part_in + (static_cast<int64_t>(part + 1) * p.tok_tile + i) * kBlockCh);
+            }
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) total[i] += static_cast<int32_t>(__float_as_uint(now[i]));
+          }
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) sums[kGroup ? 0 : i] = static_cast<float>(total[i]) * 0.0625f;
+        }
+      }
 
       // finalize: row scale, bias, gate, residual, cast, store.  Lanes hold consecutive channels -> 64 B per
       // warp store.  (A version that transposed the block through shared memory to store 16-byte vectors along
@@ -705,17 +817,38 @@ int sm_count() {
   return cached[dev] > 0 ? cached[dev] : 148;
 }
 
-// Tokens per tile: a multiple of 16 up to 128 (four drain warps x 32 columns per TMEM lane quarter).
-// Measured on B200 a 128-K group costs a fixed part (barrier and TMEM round trips, int4 unpack) plus a part
-// proportional to the tile width, roughly 150 + t "column units"; the kernel runs ceil(tiles / SMs) waves.
-int pick_tok_tile(int64_t M, int ch_tiles, int sms) {
-  if (M <= 16) return 16;
+// Cost of one 128-K block of a tile of t tokens, and what a tile and a K split add, in the same "column units"
+// (measured on B200: a block costs a fixed part - barrier and TMEM round trips, int4 unpack - plus a part
+// proportional to the tile width; set-up and finalize of a tile about 20 narrow blocks; the exchange of partial sums
+// through memory about twice that: at K = 3072 a split gains nothing, at K = 12288 it halves the time).
+constexpr double kTileCost = 3000.0, kSplitCost = 6000.0;
+inline double block_cost(int t) { return t + 150.0; }
+
+// How many parts the K blocks of a tile are split into: only by the small-tile kernels (<= 64 tokens), only when the
+// tiles leave at least half of the SMs idle, the blocks saved outweigh the exchange, and within the scratch given.
+int pick_splits(int tok_tile, int64_t tiles, int k_blocks, int sms, size_t split_bytes) {
+  if (tok_tile > 64 || tiles * 2 > sms || tiles > 128 || k_blocks < 4) return 1;
+  int splits = static_cast<int>(sms / tiles);
+  if (splits > k_blocks / 2) splits = k_blocks / 2;
+  if (splits > 15) splits = 15;  // a drain warp's field of the tile counter has four bits
+  if (splits < 2) return 1;
+  const size_t need = 1024 + static_cast<size_t>(tiles) * splits * tok_tile * kBlockCh * sizeof(float);
+  if (split_bytes < need) return 1;
+  const double saved = (k_blocks - (k_blocks + splits - 1) / splits) * block_cost(tok_tile);
+  return saved > kSplitCost ? splits : 1;
+}
+
+// Tokens per tile: a multiple of 16 up to 128 (four drain warps x 32 columns per TMEM lane quarter); the kernel runs
+// ceil(items / SMs) waves of items (tiles, or parts of tiles split along K).
+int pick_tok_tile(int64_t M, int ch_tiles, int k_blocks, int sms, size_t split_bytes) {
   int best = 16;
   double best_cost = 1e30;
   for (int t = 16; t <= 128; t += 16) {
     const int64_t tiles = static_cast<int64_t>(ch_tiles) * ((M + t - 1) / t);
-    const int64_t waves = (tiles + sms - 1) / sms;
-    const double cost = static_cast<double>(waves) * (t + 150);
+    const int splits = pick_splits(t, tiles, k_blocks, sms, split_bytes);
+    const int64_t waves = (tiles * splits + sms - 1) / sms;
+    const double blocks = static_cast<double>((k_blocks + splits - 1) / splits);
+    const double cost = static_cast<double>(waves) * (blocks * block_cost(t) + kTileCost + (splits > 1 ? kSplitCost : 0.0));
     if (cost <= best_cost) {  // ties go to the wider tile
       best_cost = cost;
       best = t;
@@ -773,7 +906,23 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   p.activation = a.activation; p.gate = a.gate; p.gate_span = a.gate_span > 0 ? a.gate_span : 1;
   p.gate_row_stride = a.gate_row_stride; p.residual = a.residual;
   const int tiles = p.ch_tiles * p.tok_tiles;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  // K split: when the tiles leave at least half of the SMs idle and a tile has K blocks to share out (not with an
+  // accumulator dump, whose per-tile sums the parts would have to add up)
+  p.splits = 1; p.partials = nullptr; p.counters = nullptr;
+  if (TOK <= 64 && a.split_workspace != nullptr && a.acc_dump == nullptr) {
+    const int splits = pick_splits(tok_tile, tiles, p.k_blocks, sm_count(), a.split_workspace_bytes);
+    if (splits >= 2) {
+      p.splits = splits;
+      p.counters = static_cast<unsigned long long*>(a.split_workspace);
+      p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a.split_workspace) + 1024);
+      if (!a.split_counters_cleared) {
+        const cudaError_t e = cudaMemsetAsync(p.counters, 0, 1024, stream);
+        if (e != cudaSuccess) return static_cast<int>(e);
+      }
+    }
+  }
+  const int items = tiles * p.splits;
+  const int grid = items < sm_count() ? items : sm_count();
   {  // never launch a register split the CTA cannot satisfy
     static int launch_regs[64] = {0};
     if (dev >= 0 && dev < 64 && launch_regs[dev] == 0) {
@@ -825,7 +974,9 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
 template <bool kGroup>
 int launch_mode(const GemmArgs& a, cudaStream_t stream) {
   const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
-  const int t = pick_tok_tile(a.M, ch_tiles, sm_count());
+  const int k_blocks = static_cast<int>((a.K + kBlockK - 1) / kBlockK);
+  const size_t split_bytes = (a.split_workspace != nullptr && a.acc_dump == nullptr) ? a.split_workspace_bytes : 0;
+  const int t = pick_tok_tile(a.M, ch_tiles, k_blocks, sm_count(), split_bytes);
   if (t <= 32) return launch_tok<32, kGroup>(a, t, stream);
   if (t <= 64) return launch_tok<64, kGroup>(a, t, stream);
   return launch_tok<128, kGroup>(a, t, stream);
@@ -924,7 +1075,7 @@ int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t st
   if (a.wscale_mode != SQ_WSCALE_GROUP_F16 || a.codes_layout != SQ_CODES_EVEN_ODD || a.out_dtype != SQ_BF16 || a.M <= 128)
     return SQ_ERR_ENUM;
   const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
-  int t = pick_tok_tile(a.M, ch_tiles, sm_count());
+  int t = pick_tok_tile(a.M, ch_tiles, static_cast<int>((a.K + kBlockK - 1) / kBlockK), sm_count(), 0);
   if (t <= 64) t = 128;
   return launch_variant<128, true, true, false, __nv_bfloat16, true>(a, t, stream, timeline);
 }

@@ -180,8 +180,11 @@ def test_gemm_group_scheme(native, oracle, m, k, n, abits):
         # same numbers up to the fp32 summation order of the drain: within one bf16 step almost everywhere
         assert rel_fro(out.cpu(), want_out) < 3e-3
         plain = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
-                            codes_layout=layout)
+                            codes_layout=layout, split=False)
         assert torch.equal(plain, out)
+        parts = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
+                            codes_layout=layout, split=True)
+        assert rel_fro(parts.cpu(), want_out) < 3e-3  # parts of a split tile add their fp32 sums in part order
         if abits == 4:  # the promise "codes within [-8, 7]" selects the small accumulator offset
             out4, acc4 = native.gemm(codes, packed, wscales, row_scales, bias.cuda(), out_dtype=torch.bfloat16,
                                      codes_layout=layout, want_accumulators=True, int4_range=True)
@@ -190,7 +193,7 @@ def test_gemm_group_scheme(native, oracle, m, k, n, abits):
 
 
 @pytest.mark.parametrize("m,k,n", [(2048, 3072, 3072), (1024, 12288, 3072), (1100, 1024, 4096), (200, 3072, 3072),
-                                   (16, 3072, 12288)])
+                                   (16, 3072, 12288), (16, 3072, 3072), (40, 12288, 3072)])
 @pytest.mark.parametrize("abits", [8, 4])
 def test_gemm_group_scheme_many_tiles(native, oracle, m, k, n, abits):
     """Group form at sizes where a persistent thread block walks several tiles (more tiles than SMs: 384 at
@@ -227,10 +230,32 @@ def test_gemm_group_scheme_many_tiles(native, oracle, m, k, n, abits):
             assert rel_fro(out[rows.cuda()].cpu(), want_out) < bar
             assert rel_fro(out, check_out) < bar
             plain = native.gemm(*args, out_dtype=torch.bfloat16, int4_range=int4_range, split=split)
-            assert torch.equal(plain, out)
+            if split:  # parts of a split tile add their fp32 sums in part order: rounding may differ from one pass
+                assert rel_fro(plain, check_out) < bar
+            else:
+                assert torch.equal(plain, out)
             again = native.gemm(*args, out_dtype=torch.bfloat16, int4_range=int4_range, split=split)
             assert torch.equal(again, plain)  # the K-split reduction does not depend on arrival order
             del out, acc
+    assert native.device_status() == 0
+
+
+@pytest.mark.parametrize("m,k,n", [(16, 3072, 3072), (33, 12288, 3072), (64, 1024, 1024), (7, 512, 136)])
+def test_channel_form_split_along_k_is_exact(native, oracle, m, k, n):
+    """Per-channel scales, few tiles: the parts of a tile split along K exchange int32 accumulators, so the output
+    is bit for bit what one pass over K gives, whichever part arrives last and however often the scratch is reused."""
+    gen = torch.Generator().manual_seed(m + k + n)
+    codes = torch.randint(-127, 128, (m, k), generator=gen, dtype=torch.int8)
+    qweight = torch.randint(-8, 8, (n, k), generator=gen, dtype=torch.int8)
+    wscales = torch.rand(n, generator=gen) * 0.01 + 0.001
+    row_scales = torch.rand(m, generator=gen) + 0.5
+    bias = (torch.randn(n, generator=gen) * 0.01).bfloat16()
+    args = (even_odd(codes).cuda(), oracle.pack_signed_int4(qweight).cuda(), wscales.cuda(), row_scales.cuda(), bias.cuda())
+    one_pass = native.gemm(*args, out_dtype=torch.bfloat16, split=False)
+    check_out, _ = native.gemm(*args, out_dtype=torch.bfloat16, want_accumulators=True, check_kernel=True)
+    assert torch.equal(one_pass, check_out)
+    for _ in range(3):
+        assert torch.equal(native.gemm(*args, out_dtype=torch.bfloat16, split=True), one_pass)
     assert native.device_status() == 0
 
 
@@ -289,7 +314,7 @@ def test_gemm_group_extreme_sums(native, oracle, code, weight, int4_range):
     assert torch.equal(acc.cpu().long(), want_acc)
     assert rel_fro(out.cpu(), want_out) < 2e-3
     plain = native.gemm(codes.cuda(), packed, wscales.cuda(), row_scales.cuda(), None, out_dtype=torch.bfloat16,
-                        codes_layout=0, int4_range=int4_range)
+                        codes_layout=0, int4_range=int4_range, split=False)
     assert torch.equal(plain, out)
 
 
