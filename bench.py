@@ -345,9 +345,24 @@ def run_nsplit(args):
         return a0.elapsed_time(a1) / args.steps
 
     serial_ms, local_ms = timed(serial), timed(lambda: local(x))
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps, serial_ms, local_ms], device=device, dtype=torch.float64)
+    # the gather fused into the GEMM: every rank's epilogue stores its block of columns into the [M, N] matrix of
+    # every rank through peer pointers (sq_gemm_scatter); no collective, no re-layout
+    shared = sharding.PeerMatrix(m, n, torch.bfloat16)
+    codes_buf = (torch.empty((m, k), device=device, dtype=torch.int8), torch.empty((m,), device=device, dtype=torch.float32))
+    fused = lambda: sharding.channel_split_linear_fused(x, packed, scales, None, shared, abits=4, signs=signs,
+                                                        workspace=codes_buf)
+    fused()
+    torch.cuda.synchronize()
+    dist.barrier()
+    fused_err = ((shared.local()[:32].cpu().float() - want.float()).norm() / want.float().norm()).item()
+    if not fused_err < 1e-2:
+        raise SystemExit(f"fused channel-split output differs from the oracle: {fused_err}")
+    fused_ms = timed(fused)
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps, serial_ms, local_ms, fused_ms], device=device, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, serial_ms, local_ms = t.tolist()
+    nccl_ms, serial_ms, local_ms, fused_ms = t.tolist()
+    shared.close()
+    ms = fused_ms
     gather_bytes = 2 * m * n * (world - 1) // world  # bytes every rank receives per step
     if rank == 0:
         print(json.dumps({
@@ -356,12 +371,16 @@ def run_nsplit(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int4 -> int32",
             "data": "synthetic",
             "config": {"workload": "nsplit_ffn_up", "M": m, "K": k, "N": n,
-                       "split": "output channels across ranks + NCCL all-gather in %d token chunks, gather(i) under GEMM(i+1)" % args.chunks,
+                       "split": "output channels across ranks; the GEMM epilogue stores its columns into every rank's "
+                                "[M, N] matrix through peer pointers (no collective)",
                        "gather_bytes_per_rank": gather_bytes},
-            "gpu_launches": 2 * args.steps * args.chunks, "parity_rel_fro": err,
-            "nsplit": {"ms_overlapped": ms, "ms_serial": serial_ms, "ms_local_gemm_only": local_ms,
-                       "gather_gbs_per_rank_if_exposed": (gather_bytes / ((ms - local_ms) * 1e-3) / 1e9) if ms > local_ms else None,
-                       "gather_ms_at_770_gbs": gather_bytes / 770e9 * 1e3}}), flush=True)
+            "gpu_launches": 2 * args.steps, "parity_rel_fro": fused_err,
+            "nsplit": {"ms_fused_peer_stores": fused_ms, "ms_nccl_all_gather_%d_chunks_overlapped" % args.chunks: nccl_ms,
+                       "ms_nccl_all_gather_serial": serial_ms, "ms_local_gemm_only": local_ms,
+                       "nccl_parity_rel_fro": err,
+                       "nvlink_gbs_per_rank_out": gather_bytes / (fused_ms * 1e-3) / 1e9,
+                       "transfer_ms_at_770_gbs": gather_bytes / 770e9 * 1e3,
+                       "frac_of_slower_bound": max(gather_bytes / 770e9 * 1e3, 2.0 * m * (n // world) * k / 3.1e15 * 1e3) / fused_ms}}), flush=True)
     dist.destroy_process_group()
 
 

@@ -33,6 +33,8 @@ _SIGNATURES = {
     "sq_gemm_split": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                               c_int64, c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "sq_split_workspace_bytes": (c_size_t, [c_int64]),
+    "sq_gemm_scatter": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+                                c_int64, c_int, c_int64, c_int64, c_int64, c_void_p]),
     "sq_gemm_check": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                               c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "sq_gemm_timeline": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

@@ -276,6 +276,26 @@ int sq_gemm_split(const void* codes, int codes_layout, const void* w_packed, con
 
 size_t sq_split_workspace_bytes(int64_t M) { return sq::gemm_split_workspace_bytes(M); }
 
+int sq_gemm_scatter(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+                    const float* row_scales, const void* bias, void* const* outs, int n_outs, int64_t out_ld,
+                    int64_t out_col0, int out_dtype, int64_t M, int64_t N, int64_t K, void* stream) {
+  if (outs == nullptr) return SQ_ERR_NULL;
+  if (n_outs < 1 || n_outs > 8) return SQ_ERR_SHAPE;
+  if (out_col0 < 0 || out_ld < out_col0 + N) return SQ_ERR_SHAPE;
+  for (int d = 0; d < n_outs; ++d) {
+    if (outs[d] == nullptr) return SQ_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(outs[d]) & 1u) != 0) return SQ_ERR_SHAPE;  // 2-byte elements
+  }
+  sq::GemmArgs a = make_args(codes, codes_layout, w_packed, w_scales, wscale_mode, row_scales, bias, outs[0], out_dtype,
+                             M, N, K, nullptr);
+  a.out_ld = out_ld;
+  a.out_col0 = out_col0;
+  a.n_more_outs = n_outs - 1;
+  for (int d = 1; d < n_outs; ++d) a.more_outs[d - 1] = outs[d];
+  if (M > 0 && M < 128) return SQ_ERR_SHAPE;  // the channel-split form is built for many tokens (128-token tiles)
+  return sq::launch_gemm_tc(a, static_cast<cudaStream_t>(stream));
+}
+
 int sq_gemm_check(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
                   const float* row_scales, const void* bias, void* out, int out_dtype, int64_t M, int64_t N,
                   int64_t K, int32_t* acc_dump, void* stream) {

@@ -109,6 +109,11 @@ struct TcParams {
   int splits;
   float* partials;
   unsigned long long* counters;
+  // output matrix: row stride and first column (a plain [M, N] output: N and 0); kScatter: the same block also
+  // goes to n_more matrices at these distances (in elements) from `out`
+  int64_t out_ld, out_col0;
+  int n_more;
+  int64_t more_delta[7];
   int offset_steps;     // group mode: constant-tile MMAs in front of every group (1 or 4)
   uint32_t offset_word;  // four copies of the constant tile's byte
   uint32_t offset_bits;  // what those MMAs add to every accumulator element
@@ -174,7 +179,8 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
 // kDump  also write the exact integer accumulators
 // kPre   the weights arrive already unpacked (int8 = 16 w, even-odd k order, from sq_prepack_weights): TMA puts
 //        them straight into the operand tile and the unpack warps have nothing to do
-template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false>
+template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
+          bool kScatter = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TcParams p) {
@@ -713,7 +719,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       // shuffles run in every lane, whether or not its channel exists.
       const bool plain = p.gate == nullptr && p.residual == nullptr;
       const bool store_ok = n_ok;
-      OutT* out = static_cast<OutT*>(p.out) + m0 * p.N + (n_ok ? n : 0);
+      OutT* out = static_cast<OutT*>(p.out) + m0 * p.out_ld + p.out_col0 + (n_ok ? n : 0);
       if (threadIdx.x == 256) stamp(kTrTileEnds, 2 * (git / groups) - 2);  // finalize begins / has ended
       if (plain) {
         // the common case is kept apart from the fused forms: a short straight run of instructions per column
@@ -728,8 +734,15 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             y = __fmul_rn(__fmul_rn(sums[kGroup ? 0 : i], rs), wscale);
           }
           if (has_bias) y = __fadd_rn(y, bias);
-          if (store_ok && i < my_cols) *out = from_float<OutT>(y);
-          out += p.N;
+          if (store_ok && i < my_cols) {
+            const OutT value = from_float<OutT>(y);
+            *out = value;
+            if (kScatter) {
+              // the same 64 bytes per warp to the other GPUs' matrices: plain stores through peer pointers
+              for (int d = 0; d < p.n_more; ++d) out[p.more_delta[d]] = value;
+            }
+          }
+          out += p.out_ld;
         }
       } else {
         // gate rows change every gate_span tokens: one division for the first column, then a running remainder
@@ -754,7 +767,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             if (residual != nullptr) y = __fadd_rn(y, to_float<OutT>(__ldg(residual)));
             *out = from_float<OutT>(y);
           }
-          out += p.N;
+          out += p.out_ld;
           if (residual != nullptr) residual += p.N;
           if (gate != nullptr && --gate_left == 0) {
             gate_left = p.gate_span;
@@ -858,9 +871,10 @@ int pick_tok_tile(int64_t M, int ch_tiles, int k_blocks, int sms, size_t split_b
   return best;
 }
 
-template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false>
+template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
+          bool kScatter = false>
 int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long long* timeline = nullptr) {
-  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre>;
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre, kScatter>;
   constexpr uint32_t smem = smem_bytes_for(TOK);
   static bool configured[64] = {false};
   int dev = 0;
@@ -903,6 +917,15 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   p.tok_tiles = static_cast<int>((a.M + tok_tile - 1) / tok_tile);
   p.k_blocks = static_cast<int>((a.K + kBlockK - 1) / kBlockK);
   p.out_dtype = a.out_dtype;
+  p.out_ld = a.out_ld > 0 ? a.out_ld : a.N;
+  p.out_col0 = a.out_ld > 0 ? a.out_col0 : 0;
+  p.n_more = kScatter ? a.n_more_outs : 0;
+  for (int d = 0; d < 7; ++d) {
+    // distance in elements between the matrices (any two addresses of the unified address space)
+    p.more_delta[d] = d < p.n_more ? (reinterpret_cast<intptr_t>(a.more_outs[d]) - reinterpret_cast<intptr_t>(a.out)) /
+                                         static_cast<intptr_t>(sizeof(OutT))
+                                   : 0;
+  }
   p.activation = a.activation; p.gate = a.gate; p.gate_span = a.gate_span > 0 ? a.gate_span : 1;
   p.gate_row_stride = a.gate_row_stride; p.residual = a.residual;
   const int tiles = p.ch_tiles * p.tok_tiles;
@@ -962,6 +985,12 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
 #define SQ_LAUNCH(EO, DUMP)                                                                          \
   (bf16 ? launch_variant<TOK, kGroup, EO, DUMP, __nv_bfloat16>(a, tok_tile, stream)          \
         : launch_variant<TOK, kGroup, EO, DUMP, __half>(a, tok_tile, stream))
+  if (a.n_more_outs > 0) {
+    // channel-split form: the 128-token kernel only (a split over GPUs is for many tokens), even-odd codes, packed weights
+    if (TOK != 128 || !eo || dump || a.weights_prepacked) return SQ_ERR_ENUM;
+    return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, true>(a, tok_tile, stream)
+                : launch_variant<128, kGroup, true, false, __half, false, false, true>(a, tok_tile, stream);
+  }
   if (a.weights_prepacked) {  // validated: even-odd codes, no accumulator dump
     return bf16 ? launch_variant<TOK, kGroup, true, false, __nv_bfloat16, false, true>(a, tok_tile, stream)
                 : launch_variant<TOK, kGroup, true, false, __half, false, true>(a, tok_tile, stream);
@@ -976,7 +1005,8 @@ int launch_mode(const GemmArgs& a, cudaStream_t stream) {
   const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
   const int k_blocks = static_cast<int>((a.K + kBlockK - 1) / kBlockK);
   const size_t split_bytes = (a.split_workspace != nullptr && a.acc_dump == nullptr) ? a.split_workspace_bytes : 0;
-  const int t = pick_tok_tile(a.M, ch_tiles, k_blocks, sm_count(), split_bytes);
+  int t = pick_tok_tile(a.M, ch_tiles, k_blocks, sm_count(), split_bytes);
+  if (a.n_more_outs > 0 && t <= 64) t = 128;  // the channel-split form exists in the 128-token kernel only
   if (t <= 32) return launch_tok<32, kGroup>(a, t, stream);
   if (t <= 64) return launch_tok<64, kGroup>(a, t, stream);
   return launch_tok<128, kGroup>(a, t, stream);

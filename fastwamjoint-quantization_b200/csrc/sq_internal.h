@@ -62,6 +62,14 @@ struct GemmArgs {
   void* split_workspace = nullptr;
   size_t split_workspace_bytes = 0;
   bool split_counters_cleared = false;  // the caller already put a memset of the first 1024 bytes on the stream
+  // Channel-split form (sq_gemm_scatter): this GPU holds N of the layer's output channels and writes its [M, N]
+  // block into columns [out_col0, out_col0 + N) of row-major [M, out_ld] matrices, `out` and up to 7 more - the
+  // same matrix on the other GPUs of the split, reached through peer pointers: the all-gather is the epilogue's
+  // own stores over NVLink.  out_ld == 0: a plain [M, N] output.
+  int64_t out_ld = 0;
+  int64_t out_col0 = 0;
+  int n_more_outs = 0;
+  void* more_outs[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 int validate_gemm(const GemmArgs& a);

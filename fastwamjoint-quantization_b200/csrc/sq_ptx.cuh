@@ -159,7 +159,7 @@ __device__ __forceinline__ bool mbar_wait_probe(uint32_t bar, uint32_t parity, v
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
-// 2-D tiled load, no multicast: box -> this CTA's shared memory, completion on `bar`.
+// 2-D tiled load into this CTA alone: box -> this CTA's shared memory, completion on `bar`.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap, int32_t x, int32_t y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

@@ -125,6 +125,25 @@ def gemm(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_
     return (out, acc) if want_accumulators else out
 
 
+def gemm_scatter(codes: torch.Tensor, packed: torch.Tensor, w_scales: torch.Tensor, row_scales: torch.Tensor, bias,
+                 out_pointers, out_ld: int, out_col0: int, *, out_dtype: torch.dtype, int4_range: bool = False):
+    """Channel-split GEMM (``sq_gemm_scatter``): this GPU's [M, N] block is stored into columns
+    ``[out_col0, out_col0 + N)`` of the row-major [M, out_ld] matrices at ``out_pointers`` - raw device addresses,
+    the first one local, the others the same matrix on the other GPUs of the split (peer pointers)."""
+    import ctypes
+    _require_cuda(codes, "codes")
+    m, k = codes.shape
+    n = packed.shape[0]
+    pointers = (ctypes.c_void_p * len(out_pointers))(*[int(ptr) for ptr in out_pointers])
+    layout = int(_lib.CODES_EVEN_ODD) | (_lib.CODES_INT4_RANGE if int4_range else 0)
+    with torch.cuda.device(codes.device):
+        status = _lib.load_library().sq_gemm_scatter(
+            codes.data_ptr(), layout, packed.data_ptr(), w_scales.data_ptr(), _wscale_mode(packed, w_scales),
+            row_scales.data_ptr(), _ptr(bias), ctypes.cast(pointers, ctypes.c_void_p), len(out_pointers), int(out_ld),
+            int(out_col0), _DTYPES[out_dtype], m, n, k, _stream())
+    _lib.check(status, "sq_gemm_scatter")
+
+
 def _rows_view(t: torch.Tensor, width: int, name: str):
     """(data pointer, row stride in elements, rows) of a tensor whose last axis is contiguous and whose leading
     axes collapse to evenly strided rows - e.g. the strided slice ``modulation[:, 0]`` of a [groups, 6, width] tensor."""

@@ -7,6 +7,9 @@
   token chunks so the gather of one chunk overlaps the GEMM of the next.  The gather moves ``2*M*N*(G-1)/G``
   bytes into every rank and is communication-bound for every shape of interest; it exists because the benchmark
   configuration names it.  Plain NCCL all-gather, no peer-memory kernels.
+* The same split with the gather fused into the GEMM (``PeerMatrix`` + ``channel_split_linear_fused``): every rank
+  maps the other ranks' output matrices (CUDA IPC) and the GEMM's epilogue stores its block of columns into all of
+  them with plain stores over NVLink (``sq_gemm_scatter``); there is no collective and no re-layout afterwards.
 
 The host-side logic (row ranges, slice ownership, gather + re-layout) is device independent and is tested
 with world-size-2 gloo process groups on CPU with a stand-in for the local linear.
@@ -77,3 +80,81 @@ def channel_split_linear(x: torch.Tensor, linear_slice: Callable[[torch.Tensor],
     if side is not None:
         torch.cuda.current_stream(x.device).wait_stream(side)
     return out.reshape(*rows_shape, out.shape[-1])
+
+
+class PeerMatrix:
+    """A row-major ``[rows, width]`` matrix of 2-byte elements that exists once per rank and is mapped into every
+    other rank of ``group`` through CUDA IPC, so that a kernel of one rank can store into all of them.
+
+    ``pointers[0]`` is this rank's own matrix, the rest are the peers' in rank order (this rank left out).  The
+    memory comes straight from ``cudaMalloc`` (an IPC handle names a whole allocation) and is released by
+    ``close()``; ``local()`` views this rank's matrix as a torch tensor."""
+
+    def __init__(self, rows: int, width: int, dtype: torch.dtype, *, group=None):
+        from cuda.bindings import runtime as rt
+
+        if dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("PeerMatrix holds bf16 or fp16.")
+        self._rt, self.rows, self.width, self.dtype, self.group = rt, int(rows), int(width), dtype, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.device = torch.cuda.current_device()
+        nbytes = max(2 * self.rows * self.width, 2)
+        err, self._ptr = rt.cudaMalloc(nbytes)
+        self._check(err, "cudaMalloc")
+        err, handle = rt.cudaIpcGetMemHandle(self._ptr)
+        self._check(err, "cudaIpcGetMemHandle")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.reserved), group=group)
+        self._peers = []
+        for rank, raw in enumerate(handles):
+            if rank == self.rank:
+                continue
+            theirs = rt.cudaIpcMemHandle_t()
+            theirs.reserved = raw
+            err, ptr = rt.cudaIpcOpenMemHandle(theirs, rt.cudaIpcMemLazyEnablePeerAccess)
+            self._check(err, f"cudaIpcOpenMemHandle(rank {rank})")
+            self._peers.append(int(ptr))
+        self.pointers = [int(self._ptr)] + self._peers
+        dist.barrier(group=group)
+
+    def _check(self, err, what):
+        if int(err) != 0:
+            raise RuntimeError(f"{what} failed with CUDA error {int(err)}.")
+
+    def local(self) -> torch.Tensor:
+        class _Raw:
+            pass
+
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (self.rows, self.width), "typestr": "<u2", "data": (int(self._ptr), False),
+                                        "version": 3, "strides": None}
+        self._keep = raw
+        return torch.as_tensor(raw, device=f"cuda:{self.device}").view(self.dtype)
+
+    def close(self):
+        """Unmap the peers' matrices and free this rank's; every rank must be done with all of them."""
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for ptr in self._peers:
+            self._rt.cudaIpcCloseMemHandle(ptr)
+        self._peers = []
+        dist.barrier(group=self.group)
+        if self._ptr is not None:
+            self._rt.cudaFree(self._ptr)
+            self._ptr = None
+
+
+def channel_split_linear_fused(x: torch.Tensor, packed_slice: torch.Tensor, scales_slice: torch.Tensor, bias_slice,
+                               out: PeerMatrix, *, abits: int, signs=None, workspace=None) -> None:
+    """Per-token quantized linear of the full ``x`` [rows, K] against this rank's slice of the weight, written into
+    this rank's block of columns of ``out`` on EVERY rank by the GEMM's own epilogue (``sq_gemm_scatter``).
+
+    Only queues work on the current stream.  The caller separates calls that reuse ``out`` (a barrier after the
+    readers are done) and waits for all ranks (stream synchronize + barrier) before reading ``out.local()``."""
+    from . import native
+
+    rows, k = x.shape
+    width = packed_slice.shape[0]
+    codes, row_scales = native.prepass(x, abits=abits, mode="token", signs=signs, out=workspace)
+    native.gemm_scatter(codes, packed_slice, scales_slice, row_scales, bias_slice, out.pointers, out.width,
+                        out.rank * width, out_dtype=out.dtype, int4_range=(abits == 4))

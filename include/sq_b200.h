@@ -137,6 +137,20 @@ int sq_gemm_split(const void* codes, int codes_layout, const void* w_packed, con
                   void* split_workspace, size_t split_workspace_bytes, void* stream);
 size_t sq_split_workspace_bytes(int64_t M);
 
+/* sq_gemm for a layer whose output channels are split over GPUs (one process per GPU; this GPU holds rows
+ * [out_col0, out_col0 + N) of the layer's weight matrix): the [M, N] block goes into columns
+ * [out_col0, out_col0 + N) of row-major [M, out_ld] matrices, outs[0] on this GPU and outs[1 .. n_outs) the same
+ * matrix on the other GPUs, given as peer pointers (CUDA IPC or any other peer mapping).  The epilogue stores every
+ * 64-byte run of a row to all of them, so the all-gather that would follow the GEMM (ncclAllGather plus a local
+ * permute into the [M, out_ld] layout) is the GEMM's own NVLink traffic and overlaps its tensor-core work tile by
+ * tile.  Plain stores only: no TMA and no multicast touches peer memory.  The caller orders the GPUs around the call
+ * (nobody may read a matrix before every GPU's kernel has finished; nobody may start the next call's stores
+ * before every reader is done).  M >= 128; packed int4 weights; even-odd codes; bf16 or fp16 output.
+ * The reference has no counterpart (it runs on one GPU). */
+int sq_gemm_scatter(const void* codes, int codes_layout, const void* w_packed, const void* w_scales, int wscale_mode,
+                    const float* row_scales, const void* bias, void* const* outs, int n_outs, int64_t out_ld,
+                    int64_t out_col0, int out_dtype, int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Plain-CUDA-core version of sq_gemm with the same arguments (SQ_CODES_INT4_RANGE is accepted and ignored), the
  * same accumulators and, in the group form, the oracle's own fp32 summation order.  It exists so the
  * tensor-core kernel can be cross-checked on the device; it is not a fallback and nothing dispatches to it. */

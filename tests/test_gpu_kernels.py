@@ -240,6 +240,33 @@ def test_gemm_group_scheme_many_tiles(native, oracle, m, k, n, abits):
     assert native.device_status() == 0
 
 
+@pytest.mark.parametrize("group", [True, False])
+def test_channel_split_epilogue_writes_its_columns_into_every_matrix(native, oracle, group):
+    """sq_gemm_scatter: the [M, N] block of a GPU that holds N of a layer's channels goes into columns
+    [col0, col0 + N) of every [M, ld] matrix it is given (here two matrices on one GPU stand in for the peers);
+    the values are those of the plain GEMM bit for bit and nothing outside the block is touched."""
+    m, k, n, ld, col0 = 300, 1024, 256, 1024, 512
+    gen = torch.Generator().manual_seed(11)
+    codes = torch.randint(-7, 8, (m, k), generator=gen, dtype=torch.int8)
+    qweight = torch.randint(-8, 8, (n, k), generator=gen, dtype=torch.int8)
+    wscales = ((torch.rand(n, k // 128, generator=gen) * 0.01 + 0.001).half() if group
+               else torch.rand(n, generator=gen) * 0.01 + 0.001)
+    row_scales = torch.rand(m, generator=gen) + 0.5
+    bias = (torch.randn(n, generator=gen) * 0.01).bfloat16()
+    args = (even_odd(codes).cuda(), oracle.pack_signed_int4(qweight).cuda(), wscales.cuda(), row_scales.cuda(), bias.cuda())
+    plain = native.gemm(*args, out_dtype=torch.bfloat16, int4_range=True, split=False)
+    first = torch.full((m, ld), 7.0, device="cuda", dtype=torch.bfloat16)
+    second = torch.full((m, ld), 7.0, device="cuda", dtype=torch.bfloat16)
+    native.gemm_scatter(*args, [first.data_ptr(), second.data_ptr()], ld, col0, out_dtype=torch.bfloat16, int4_range=True)
+    torch.cuda.synchronize()
+    for matrix in (first, second):
+        assert torch.equal(matrix[:, col0:col0 + n], plain)
+        assert bool((matrix[:, :col0] == 7.0).all()) and bool((matrix[:, col0 + n:] == 7.0).all())
+    with pytest.raises(RuntimeError):
+        native.gemm_scatter(*args, [first.data_ptr()], ld, ld - n + 8, out_dtype=torch.bfloat16)  # block past the row end
+    assert native.device_status() == 0
+
+
 @pytest.mark.parametrize("m,k,n", [(16, 3072, 3072), (33, 12288, 3072), (64, 1024, 1024), (7, 512, 136)])
 def test_channel_form_split_along_k_is_exact(native, oracle, m, k, n):
     """Per-channel scales, few tiles: the parts of a tile split along K exchange int32 accumulators, so the output
