@@ -206,7 +206,9 @@ def run_sweep(args):
             for m in (16, 64, 256, 1024, 4096, 16384, 32768):
                 x = torch.randn(m, k, device=device, generator=gen).bfloat16()
                 out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
-                work = torch.empty(native._lib.load_library().sq_workspace_bytes(m, k), device=device, dtype=torch.uint8)
+                lib = native._lib.load_library()
+                # room for the K-split scratch too: with few tiles (small M) the kernel splits a tile's K blocks
+                work = torch.empty(lib.sq_workspace_bytes(m, k) + lib.sq_split_workspace_bytes(m), device=device, dtype=torch.uint8)
                 weight = tiled if tiled is not None and m >= 512 else packed  # the int8 copy only pays above the ridge
                 ms = _time_graph(lambda: native.linear(x, weight, scales, None, abits=abits, mode="token", signs=signs,
                                                        out=out, workspace=work), 20 if m <= 4096 else 5)
@@ -745,6 +747,26 @@ def main():
     h1.record()
     barrier()
     e2e_ms = h0.elapsed_time(h1)
+
+    # what the host link alone allows: the same two copies per step on the same streams and buffers, no kernel
+    def copies_only(count):
+        for i in range(count):
+            b = i % depth
+            with torch.cuda.stream(copy_in):
+                x_dev[b].copy_(x_host[b], non_blocking=True)
+            with torch.cuda.stream(copy_out):
+                out_host[b].copy_(out_dev[b], non_blocking=True)
+        main.wait_stream(copy_in)
+        main.wait_stream(copy_out)
+
+    copies_only(4)
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    copies_only(e2e_steps)
+    c1.record()
+    barrier()
+    copy_ms = c0.elapsed_time(c1)
     e2e_err = ((out_host[0][:rows].float() - want.float()).norm() / want.float().norm()).item()
     if not e2e_err < 1e-2:
         raise SystemExit(f"end-to-end output differs from the oracle: relative Frobenius error {e2e_err}")
@@ -754,9 +776,9 @@ def main():
         raise SystemExit(f"a kernel gave up a bounded wait: device status {status}")
 
     if distributed:
-        t = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+        t = torch.tensor([elapsed_ms, e2e_ms, copy_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = t.tolist()
+        elapsed_ms, e2e_ms, copy_ms = t.tolist()
 
     ops_per_step = 2.0 * m * n * k
     tops = world * ops_per_step * args.steps / (elapsed_ms * 1e-3) / 1e12
@@ -817,7 +839,10 @@ def main():
             "gpu_launches": 2 * args.steps * replays,
             "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": x_host[0].numel() * 2,
                     "d2h_bytes_per_step": out_host[0].numel() * 2, "ms_per_step": e2e_ms / e2e_steps,
-                    "pipeline": "host->device copy, linear and device->host copy of consecutive steps overlap (3 streams, 2 buffers)"},
+                    "pipeline": "host->device copy, linear and device->host copy of consecutive steps overlap (3 streams, 2 buffers)",
+                    "copies_only_ms_per_step": copy_ms / e2e_steps,
+                    "host_link_gbs_each_way": x_host[0].numel() * 2 / (copy_ms / e2e_steps * 1e-3) / 1e9,
+                    "frac_of_host_link_ceiling": copy_ms / e2e_ms},
             "roofline": roofline, "clocks": clocks, "parity_rel_fro": err,
         }
         if not args.no_cpu_baseline and world == 1:  # reported at N = 1 only: the other ranks would share the cores
