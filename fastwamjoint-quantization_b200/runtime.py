@@ -187,9 +187,17 @@ class WAMQuantLinear(nn.Module):
             self._weight_tiled = native.prepack_weights(self.weight.contiguous())
         return self
 
-    def _native_weight(self) -> torch.Tensor:
+    PREPACK_MIN_ROWS = 512  # below this the GEMM is bound by weight bytes, which the unpacked form doubles
+
+    def _native_weight(self, rows: int | None = None) -> torch.Tensor:
+        """The packed checkpoint-format weight, or its kernel-native copy when there is one and the call has
+        enough input rows for the GEMM to be compute-bound."""
         tiled = getattr(self, "_weight_tiled", None)
-        return self.weight if tiled is None or tiled.device != self.weight.device else tiled
+        if tiled is None or tiled.device != self.weight.device:
+            return self.weight
+        if rows is not None and rows < self.PREPACK_MIN_ROWS:
+            return self.weight
+        return tiled
 
     def _call(self, x: torch.Tensor):
         """The active call for a native launch: the Python index, or - when the state is ``on_device`` - the
@@ -204,7 +212,7 @@ class WAMQuantLinear(nn.Module):
         layout = self._layout(x, "checkpoint")
         if self.backend != "reference":
             call = self._call(x)
-            args = (x, self._native_weight(), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges,
+            args = (x, self._native_weight(x.numel() // x.shape[-1]), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges,
                     self.gamma_gains, layout.token_counts, call)
             if self.input_rotation_signs is not None:
                 return self._native_ops.symmetric_scheduled_stream_rht_linear(
@@ -239,7 +247,7 @@ class WAMQuantLinear(nn.Module):
             raise RuntimeError("WAM AdaLN block fusion was not enabled for this site.")
         layout = self._layout(x, "fused AdaLN")
         return self._native_ops.symmetric_scheduled_stream_adaln_linear(
-            x, self._native_weight(), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
+            x, self._native_weight(x.numel() // x.shape[-1]), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
             layout.token_counts, self._call(x), scale, shift, epsilon)
 
     def forward_gate_residual(self, x, residual, gate):
@@ -247,7 +255,7 @@ class WAMQuantLinear(nn.Module):
             raise RuntimeError("WAM gate/residual block fusion was not enabled for this site.")
         layout = self._layout(x, "fused residual")
         return self._native_ops.symmetric_scheduled_stream_gate_residual_linear(
-            x, self._native_weight(), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
+            x, self._native_weight(x.numel() // x.shape[-1]), self.weight_scales, self.bias, self.input_scale, self.clipping_ranges, self.gamma_gains,
             layout.token_counts, self._call(x), residual, gate)
 
 

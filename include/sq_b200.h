@@ -121,13 +121,14 @@ int sq_gemm(const void* codes, int codes_layout, const void* w_packed, const voi
             int64_t M, int64_t N, int64_t K, int32_t* acc_dump, void* stream);
 
 /* sq_gemm with scratch for tiles that are split along K.  Whole output tiles (128 channels x up to 128 tokens)
- * are dealt round-robin to one persistent thread block per SM; when the tile count is no multiple of the SM
- * count - in particular with fewer tiles than SMs, the small-M regime of the reference (M = 32 ... 360,
- * w4a8.cu:1038-1076 picks its tile shapes for it) - the remainder is cut into K ranges so that every SM gets the
- * same number of 128-K blocks.  Each thread block parks its partial sums (fp32) in `split_workspace`; the one that
- * arrives last at a tile adds them in K order (the result does not depend on the arrival order) and finishes the
- * tile.  Integer accumulators are unchanged; group-form outputs differ from the unsplit kernel by fp32 rounding
- * only, channel-form outputs not at all (the partial sums are exact integers).
+ * are dealt round-robin to one persistent thread block per SM.  With few tokens - the small-M regime of the
+ * reference (M = 32 ... 360, w4a8.cu:1038-1076 picks its tile shapes for it) - there are fewer tiles than SMs; when
+ * the tiles (of at most 64 tokens) leave at least half of the SMs idle and a tile has enough 128-K blocks for the
+ * exchange to pay (K >= 6144 in practice), a tile's K blocks are cut into up to 15 parts, one thread block each.
+ * Every part parks its partial sums in `split_workspace`; the one that arrives last at the tile's counter adds
+ * them in part order (the result does not depend on the arrival order) and finishes the tile; nobody waits.
+ * Integer accumulators are unchanged; group-form outputs differ from the unsplit kernel by fp32 rounding only,
+ * channel-form outputs not at all (the partial sums are exact integers).  With acc_dump the kernel never splits.
  *   split_workspace        16-byte aligned, sq_split_workspace_bytes(M) bytes, or null (then this is sq_gemm).
  *                          Its first 1024 bytes are counters; this call puts a memset of them on `stream`.
  * The reference has no counterpart: its CUTLASS GEMMs never split K. */
