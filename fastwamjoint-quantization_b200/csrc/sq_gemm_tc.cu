@@ -49,8 +49,15 @@ constexpr int kThreads = 768;  // 4 control + 4 unpack + 16 drain warps
 // Register targets per role after setmaxnreg (control 24, unpack 40, drain 104).  setmaxnreg.inc only hands out
 // registers the CTA was launched with and waits for ever when the targets add up to more, so the launcher
 // checks this sum against (registers per thread at launch) x kThreads before every launch.
-constexpr int kRegsControl = 32, kRegsUnpack = 48, kRegsDrain = 96;
-constexpr int kRegisterPoolNeeded = 4 * 32 * kRegsControl + 4 * 32 * kRegsUnpack + 16 * 32 * kRegsDrain;
+// Registers per thread after the roles re-partition the CTA's allocation (setmaxnreg).  `wide_drain`: the variant of
+// the 128-token kernel that can split K keeps a few more values live in its drain loop and takes the registers for
+// them from the other roles.
+__host__ __device__ constexpr int regs_control(bool wide_drain) { return wide_drain ? 24 : 32; }
+__host__ __device__ constexpr int regs_unpack(bool wide_drain) { return wide_drain ? 40 : 48; }
+__host__ __device__ constexpr int regs_drain(bool wide_drain) { return wide_drain ? 104 : 96; }
+__host__ __device__ constexpr int register_pool_needed(bool wide_drain) {
+  return 4 * 32 * regs_control(wide_drain) + 4 * 32 * regs_unpack(wide_drain) + 16 * 32 * regs_drain(wide_drain);
+}
 constexpr uint32_t kPackedBytes = kBlockCh * kBlockK / 2;  // 8 KiB
 constexpr uint32_t kWBytes = kBlockCh * kBlockK;           // 16 KiB
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
@@ -180,7 +187,7 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
 // kPre   the weights arrive already unpacked (int8 = 16 w, even-odd k order, from sq_prepack_weights): TMA puts
 //        them straight into the operand tile and the unpack warps have nothing to do
 template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
-          bool kScatter = false>
+          bool kScatter = false, bool kSplit = (TOK <= 64)>
 __global__ void __launch_bounds__(kThreads, 1)
 sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TcParams p) {
@@ -256,8 +263,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int num_tiles = p.ch_tiles * p.tok_tiles;
-  // K is split only by the small-tile kernels (few tokens: few tiles); the 128-token kernel carries none of that code
-  constexpr bool kSplitK = TOK <= 64;
+  // K is split by the small-tile kernels (few tokens: few tiles) and by a variant of the 128-token kernel built for
+  // it; the 128-token kernel that large problems run carries none of that code
+  constexpr bool kSplitK = kSplit;
+  constexpr bool kWideDrain = kSplit && TOK == 128;
   const int splits = kSplitK ? p.splits : 1;
   const int num_items = num_tiles * splits;
   // a work item is a tile, or one part of a tile's K blocks: [kb0, kb1)
@@ -281,7 +290,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 
   if (warp < 4) {
     // ------------------------------------------------------------------ control warpgroup
-    reg_dec<kRegsControl>();
+    reg_dec<regs_control(kWideDrain)>();
     // Both roles keep the whole warp in the loop and pick the issuing thread with elect.sync: TMA and
     // tcgen05 instructions take warp-uniform operands, and only an elected region lets the compiler keep
     // them in uniform registers (a plain `lane == 0` branch costs about a hundred cycles per instruction).
@@ -402,7 +411,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ converter warpgroup
-    reg_dec<kRegsUnpack>();
+    reg_dec<regs_unpack(kWideDrain)>();
     const int ctid = threadIdx.x - 128;  // 0..127
     uint32_t it = 0;
     bool ok = true;
@@ -463,7 +472,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ drain warpgroups
-    reg_inc<kRegsDrain>();
+    reg_inc<regs_drain(kWideDrain)>();
     const int dwarp = warp - 8;           // 0..15
     const int quarter = warp & 3;         // TMEM lane quarter this warp may address
     const int slice = dwarp >> 2;         // which slice of the token columns (four warps per lane quarter)
@@ -667,6 +676,21 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (lane == 0) atomicAdd(p.counters + tile, ~(static_cast<unsigned long long>(splits) << (4 * dwarp)) + 1ull);
         const float* part_in = p.partials + (static_cast<int64_t>(tile) * splits * p.tok_tile + my_col0) * kBlockCh + ch_in_tile;
         if (kGroup) {
+          if constexpr (kCols > 16) {
+            // wide slices: no room for a second set of loads in flight; the 32 loads of one part still overlap
+            float total[kCols];
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) total[i] = 0.0f;
+            for (int part = 0; part < splits; ++part) {
+#pragma unroll
+              for (int i = 0; i < kCols; ++i)
+                if (i < my_cols)
+                  total[i] = __fadd_rn(total[i], __ldcg(part_in + (static_cast<int64_t>(part) * p.tok_tile + i) * kBlockCh));
+            }
+#pragma unroll
+            for (int i = 0; i < kCols; i += 2) sums2[kGroup ? i / 2 : 0] = pack2(total[i], total[i + 1]);
+            offset_sum = 0.0f;
+          } else {
           // the loads of the next part are in flight while this part is added (parts are added in part order)
           float total[kCols], ahead[kCols];
 #pragma unroll
@@ -688,6 +712,19 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 #pragma unroll
           for (int i = 0; i < kCols; i += 2) sums2[kGroup ? i / 2 : 0] = pack2(total[i], total[i + 1]);
           offset_sum = 0.0f;
+          }
+        } else if constexpr (kCols > 16) {
+          int32_t total[kCols];
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) total[i] = 0;
+          for (int part = 0; part < splits; ++part) {
+#pragma unroll
+            for (int i = 0; i < kCols; ++i)
+              if (i < my_cols)
+                total[i] += static_cast<int32_t>(__float_as_uint(__ldcg(part_in + (static_cast<int64_t>(part) * p.tok_tile + i) * kBlockCh)));
+          }
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) sums[kGroup ? 0 : i] = static_cast<float>(total[i]) * 0.0625f;
         } else {
           int32_t total[kCols];
           float ahead[kCols];
@@ -837,10 +874,10 @@ int sm_count() {
 constexpr double kTileCost = 3000.0, kSplitCost = 6000.0;
 inline double block_cost(int t) { return t + 150.0; }
 
-// How many parts the K blocks of a tile are split into: only by the small-tile kernels (<= 64 tokens), only when the
-// tiles leave at least half of the SMs idle, the blocks saved outweigh the exchange, and within the scratch given.
+// How many parts the K blocks of a tile are split into: only when the tiles leave at least half of the SMs idle, the
+// blocks saved outweigh the exchange, and within the scratch given.
 int pick_splits(int tok_tile, int64_t tiles, int k_blocks, int sms, size_t split_bytes) {
-  if (tok_tile > 64 || tiles * 2 > sms || tiles > 128 || k_blocks < 4) return 1;
+  if (tiles * 2 > sms || tiles > 128 || k_blocks < 4) return 1;
   int splits = static_cast<int>(sms / tiles);
   if (splits > k_blocks / 2) splits = k_blocks / 2;
   if (splits > 15) splits = 15;  // a drain warp's field of the tile counter has four bits
@@ -872,9 +909,9 @@ int pick_tok_tile(int64_t M, int ch_tiles, int k_blocks, int sms, size_t split_b
 }
 
 template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
-          bool kScatter = false>
+          bool kScatter = false, bool kSplit = (TOK <= 64)>
 int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long long* timeline = nullptr) {
-  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre, kScatter>;
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre, kScatter, kSplit>;
   constexpr uint32_t smem = smem_bytes_for(TOK);
   static bool configured[64] = {false};
   int dev = 0;
@@ -932,7 +969,7 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   // K split: when the tiles leave at least half of the SMs idle and a tile has K blocks to share out (not with an
   // accumulator dump, whose per-tile sums the parts would have to add up)
   p.splits = 1; p.partials = nullptr; p.counters = nullptr;
-  if (TOK <= 64 && a.split_workspace != nullptr && a.acc_dump == nullptr) {
+  if (kSplit && a.split_workspace != nullptr && a.acc_dump == nullptr) {
     const int splits = pick_splits(tok_tile, tiles, p.k_blocks, sm_count(), a.split_workspace_bytes);
     if (splits >= 2) {
       p.splits = splits;
@@ -955,7 +992,7 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
       launch_regs[dev] = attr.numRegs;
     }
     const int regs = (dev >= 0 && dev < 64) ? launch_regs[dev] : 0;
-    if (regs * kThreads < kRegisterPoolNeeded) return SQ_ERR_DRIVER;
+    if (regs * kThreads < register_pool_needed(kSplit && TOK == 128)) return SQ_ERR_DRIVER;
   }
   cudaError_t err;
   if (a.after_prepass) {
@@ -994,6 +1031,14 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
   if (a.weights_prepacked) {  // validated: even-odd codes, no accumulator dump
     return bf16 ? launch_variant<TOK, kGroup, true, false, __nv_bfloat16, false, true>(a, tok_tile, stream)
                 : launch_variant<TOK, kGroup, true, false, __half, false, true>(a, tok_tile, stream);
+  }
+  if (TOK == 128 && eo && !dump && a.split_workspace != nullptr) {
+    // few tiles of many K blocks (a few hundred tokens into a narrow layer): the variant of the 128-token kernel
+    // that can split K
+    const int64_t tiles = static_cast<int64_t>((a.N + kBlockCh - 1) / kBlockCh) * ((a.M + tok_tile - 1) / tok_tile);
+    if (pick_splits(tok_tile, tiles, static_cast<int>((a.K + kBlockK - 1) / kBlockK), sm_count(), a.split_workspace_bytes) >= 2)
+      return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, false, true>(a, tok_tile, stream)
+                  : launch_variant<128, kGroup, true, false, __half, false, false, false, true>(a, tok_tile, stream);
   }
   if (eo) return dump ? SQ_LAUNCH(true, true) : SQ_LAUNCH(true, false);
   return dump ? SQ_LAUNCH(false, true) : SQ_LAUNCH(false, false);

@@ -1040,9 +1040,9 @@ int launch_wait_probe(int64_t limit_us, long long* waited_ns, cudaStream_t strea
 size_t gemm_split_workspace_bytes(int64_t M) {
   if (M <= 0) return 0;
   // enough for either kernel: this one's two partial tiles per thread block, or the first-generation kernel's one
-  // part of a tile of up to 64 tokens per thread block
+  // part of a tile of up to 128 tokens per thread block
   const size_t here = split_bytes_for(pick_tok_tile(M), sm_count());
-  const int64_t tokens = M < 64 ? ((M + 15) / 16) * 16 : 64;
+  const int64_t tokens = M < 128 ? ((M + 15) / 16) * 16 : 128;
   const size_t first = 1024 + static_cast<size_t>(sm_count()) * static_cast<size_t>(tokens) * kBlockCh * sizeof(float);
   return here > first ? here : first;
 }

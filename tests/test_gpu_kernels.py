@@ -193,7 +193,7 @@ def test_gemm_group_scheme(native, oracle, m, k, n, abits):
 
 
 @pytest.mark.parametrize("m,k,n", [(2048, 3072, 3072), (1024, 12288, 3072), (1100, 1024, 4096), (200, 3072, 3072),
-                                   (16, 3072, 12288), (16, 3072, 3072), (40, 12288, 3072)])
+                                   (16, 3072, 12288), (16, 3072, 3072), (40, 12288, 3072), (294, 14336, 3072)])
 @pytest.mark.parametrize("abits", [8, 4])
 def test_gemm_group_scheme_many_tiles(native, oracle, m, k, n, abits):
     """Group form at sizes where a persistent thread block walks several tiles (more tiles than SMs: 384 at
@@ -267,7 +267,8 @@ def test_channel_split_epilogue_writes_its_columns_into_every_matrix(native, ora
     assert native.device_status() == 0
 
 
-@pytest.mark.parametrize("m,k,n", [(16, 3072, 3072), (33, 12288, 3072), (64, 1024, 1024), (7, 512, 136)])
+@pytest.mark.parametrize("m,k,n", [(16, 3072, 3072), (33, 12288, 3072), (64, 1024, 1024), (7, 512, 136),
+                                   (294, 14336, 3072), (360, 12288, 3072)])
 def test_channel_form_split_along_k_is_exact(native, oracle, m, k, n):
     """Per-channel scales, few tiles: the parts of a tile split along K exchange int32 accumulators, so the output
     is bit for bit what one pass over K gives, whichever part arrives last and however often the scratch is reused."""
