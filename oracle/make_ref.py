@@ -19,7 +19,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 TARGET = HERE / "_ref"
 PACKAGE = "fastwam_steerquant"
-DEFAULT_CHECKOUT = os.environ.get("SQ_REFERENCE_CHECKOUT", "/root/reference")
+# the checkout named by SQ_REFERENCE_CHECKOUT, else a directory "reference" beside this repository
+DEFAULT_CHECKOUT = os.environ.get("SQ_REFERENCE_CHECKOUT", str(HERE.parents[1] / "reference"))
 
 
 def make_ref(reference: Path) -> Path | None:
