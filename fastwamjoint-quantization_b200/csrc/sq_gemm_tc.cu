@@ -538,6 +538,15 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (scale_vectors) {
           chunk = __ldg(reinterpret_cast<const uint4*>(my_scales) + (g0 >> 3));
           if (8 * ((g0 >> 3) + 1) < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + (g0 >> 3) + 1);
+          {
+            // the scale in use is always the lowest half of `chunk`: drop the halves in front of group g0
+            for (int skip = 0; skip < (g0 & 7); ++skip) {
+              chunk.x = __funnelshift_r(chunk.x, chunk.y, 16);
+              chunk.y = __funnelshift_r(chunk.y, chunk.z, 16);
+              chunk.z = __funnelshift_r(chunk.z, chunk.w, 16);
+              chunk.w >>= 16;
+            }
+          }
         } else {
           // raw_a holds the scale of the next even group, raw_b of the next odd one
           const unsigned short first = __ldg(my_scales + g0);
@@ -592,13 +601,18 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (kGroup) {
           unsigned short raw;
           if (scale_vectors) {
-            const int e = g & 7;
-            const uint32_t word = e < 4 ? (e < 2 ? chunk.x : chunk.y) : (e < 6 ? chunk.z : chunk.w);
-            raw = static_cast<unsigned short>((e & 1) != 0 ? word >> 16 : word & 0xFFFFu);
-            if (e == 7) {
+            // the lowest half of the chunk is this group's scale; the chunk then moves down by one half (four
+            // funnel shifts instead of picking a half out of four registers by the group index)
+            raw = static_cast<unsigned short>(chunk.x & 0xFFFFu);
+            if ((g & 7) == 7) {
               chunk = chunk_next;
               const int c2 = (g >> 3) + 2;
               if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+            } else {
+              chunk.x = __funnelshift_r(chunk.x, chunk.y, 16);
+              chunk.y = __funnelshift_r(chunk.y, chunk.z, 16);
+              chunk.z = __funnelshift_r(chunk.z, chunk.w, 16);
+              chunk.w >>= 16;
             }
           } else {
             raw = (g & 1) == 0 ? raw_a : raw_b;
