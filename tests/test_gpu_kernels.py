@@ -240,6 +240,34 @@ def test_gemm_group_scheme_many_tiles(native, oracle, m, k, n, abits):
     assert native.device_status() == 0
 
 
+@pytest.mark.parametrize("abits", [8, 4])
+def test_gemm_at_the_largest_benchmark_size_rows_are_independent(native, oracle, abits):
+    """M = 32768, K = 3072, N = 12288 (the largest shape of the benchmark sweep; 24 576 tiles, 166 per SM): too large
+    to dump every accumulator, so the check uses what does not depend on size - every output row depends on its
+    own codes only.  Slices of 128-aligned and of ragged row ranges, run on their own (where accumulators ARE
+    checked against the cross-check kernel), must give the same output bits as the same rows of the full run."""
+    m, k, n = 32768, 3072, 12288
+    gen = torch.Generator(device="cuda").manual_seed(abits)
+    lim = 8 if abits == 4 else 128
+    codes = torch.randint(-lim + 1, lim, (m, k), generator=gen, device="cuda", dtype=torch.int8)
+    qweight = torch.randint(-8, 8, (n, k), generator=torch.Generator().manual_seed(1), dtype=torch.int8)
+    packed = oracle.pack_signed_int4(qweight).cuda()
+    wscales = (torch.rand(n, k // 128, generator=gen, device="cuda") * 0.01 + 0.001).half()
+    row_scales = torch.rand(m, generator=gen, device="cuda") + 0.5
+    full = native.gemm(codes, packed, wscales, row_scales, None, out_dtype=torch.bfloat16, int4_range=(abits == 4))
+    for lo, hi in ((0, 256), (16383, 16384 + 130), (m - 300, m)):
+        rows, scales = codes[lo:hi].clone(), row_scales[lo:hi].clone()  # fresh allocations: aligned like any tensor
+        part, acc = native.gemm(rows, packed, wscales, scales, None, out_dtype=torch.bfloat16,
+                                int4_range=(abits == 4), want_accumulators=True)
+        check_out, check_acc = native.gemm(rows, packed, wscales, scales, None, out_dtype=torch.bfloat16,
+                                           want_accumulators=True, check_kernel=True)
+        assert torch.equal(acc, check_acc)
+        assert torch.equal(full[lo:hi], part)
+        assert rel_fro(part, check_out) < 3e-3
+        del part, acc, check_out, check_acc
+    assert native.device_status() == 0
+
+
 @pytest.mark.parametrize("group", [True, False])
 def test_channel_split_epilogue_writes_its_columns_into_every_matrix(native, oracle, group):
     """sq_gemm_scatter: the [M, N] block of a GPU that holds N of a layer's channels goes into columns
