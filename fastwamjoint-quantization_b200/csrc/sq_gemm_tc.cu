@@ -179,6 +179,45 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
   atomicCAS(status, 0, code);
 }
 
+// One group of the drain (group form, chunked scales, no K split) with the accumulator ring position POS a
+// compile-time constant: barrier addresses, TMEM columns and the ring's phase then cost no instructions.  `g` is the
+// group index of position 0 of the round (a multiple of four).  Returns false when the wait gave up.
+template <uint32_t POS, int kCols>
+__device__ __forceinline__ bool drain_group_static(uint32_t bar_acc_full, uint32_t bar_acc_empty, uint32_t tmem_slice,
+                                                   uint32_t phase, volatile int* abort_flag, int lane,
+                                                   bool& acc_ready, uint4& chunk, uint4& chunk_next,
+                                                   const unsigned short* my_scales, int groups, int g,
+                                                   float offset_float, float& offset_sum, uint64_t (&sums2)[kCols / 2]) {
+  if (!acc_ready && !mbar_wait_bounded(bar_acc_full + 8 * POS, phase, abort_flag, 1000ull * 1000ull * 1000ull)) return false;
+  tc_fence_after_sync();
+  uint32_t r[kCols];
+  tmem_ld_chunk(tmem_slice + POS * 128u, r);
+  // the next group's barrier is probed under the load (a probe takes over a hundred cycles to answer)
+  acc_ready = mbar_test_wait(bar_acc_full + 8 * ((POS + 1u) & 3u), POS == 3u ? phase ^ 1u : phase);
+  // the lowest half of the chunk is this group's scale; the chunk then moves down by one half
+  const unsigned short raw = static_cast<unsigned short>(chunk.x & 0xFFFFu);
+  if (POS == 3u && (g & 4) != 0) {  // group g + 3 was the last of its chunk
+    chunk = chunk_next;
+    const int c2 = ((g + 3) >> 3) + 2;
+    if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+  } else {
+    chunk.x = __funnelshift_r(chunk.x, chunk.y, 16);
+    chunk.y = __funnelshift_r(chunk.y, chunk.z, 16);
+    chunk.z = __funnelshift_r(chunk.z, chunk.w, 16);
+    chunk.w >>= 16;
+  }
+  const float scale = __half2float(__ushort_as_half(raw)) * 7.922816251426434e28f;  // 2^96 (kScaleUp)
+  offset_sum = fmaf(offset_float, scale, offset_sum);
+  tmem_wait_ld();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_acc_empty + 8 * POS);
+  const uint64_t scale2 = pack2(scale, scale);
+#pragma unroll
+  for (int i = 0; i < kCols; i += 2) ffma2(sums2[i / 2], r[i], r[i + 1], scale2);
+  return true;
+}
+
 // TOK    capacity in tokens of one tile (TMEM columns per accumulator, rows of a codes stage); the
 //        tile actually used, p.tok_tile <= TOK, is chosen per call so the tiles fill the SMs evenly
 // kGroup one accumulator per 128-K weight group (fp16 scales [N, K/128]); otherwise one per tile (fp32 [N])
@@ -187,7 +226,7 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
 // kPre   the weights arrive already unpacked (int8 = 16 w, even-odd k order, from sq_prepack_weights): TMA puts
 //        them straight into the operand tile and the unpack warps have nothing to do
 template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
-          bool kScatter = false, bool kSplit = (TOK <= 64)>
+          bool kScatter = false, bool kSplit = (TOK <= 64), bool kStatic = false>
 __global__ void __launch_bounds__(kThreads, 1)
 sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TcParams p) {
@@ -556,7 +595,38 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         }
       }
 
-      for (int g = g0; g < g1 && ok; ++g, ++git) {
+      if constexpr (kStatic) {
+        // The launcher picks this variant when every tile has a multiple of eight groups in chunked scales and K is
+        // not split: four groups per round, each with its place in the accumulator ring a compile-time constant.
+        // The instructions a drain warp spends per group are what bounds this kernel.
+        if (my_cols > 0) {
+          uint32_t phase = (git >> 2) & 1u;
+          const uint32_t tmem_slice = tmem_base + lane_addr + my_col0;
+          for (int g = g0; g < g1 && ok; g += 4, git += 4) {
+            ok = drain_group_static<0u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
+                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2) &&
+                 drain_group_static<1u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
+                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2) &&
+                 drain_group_static<2u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
+                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2) &&
+                 drain_group_static<3u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
+                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2);
+            phase ^= 1u;
+          }
+        } else {
+          // a warp whose columns lie beyond the tile's tokens only keeps the accumulator hand-over going
+          for (int g = g0; g < g1 && ok; ++g, ++git) {
+            const uint32_t buf = git & 3u;
+            ok = mbar_wait_bounded(bar_acc_full + 8 * buf, (git >> 2) & 1u, abort_flag, kWaitLimitNs);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+          }
+          acc_ready = false;
+        }
+        if (!ok && lane == 0) report_timeout(p.status, abort_flag, 9005);
+      }
+      for (int g = g0; !kStatic && g < g1 && ok; ++g, ++git) {
         // channel form: the tile's accumulator pair (2j, 2j + 1), the second in use when the issuers split K
         const uint32_t buf = kGroup ? git % kAccBufs : (git & 1u) * 2u;
         const uint32_t aphase = kGroup ? (git / kAccBufs) & 1u : (git >> 1) & 1u;
@@ -923,9 +993,9 @@ int pick_tok_tile(int64_t M, int ch_tiles, int k_blocks, int sms, size_t split_b
 }
 
 template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
-          bool kScatter = false, bool kSplit = (TOK <= 64)>
+          bool kScatter = false, bool kSplit = (TOK <= 64), bool kStatic = false>
 int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long long* timeline = nullptr) {
-  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre, kScatter, kSplit>;
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre, kScatter, kSplit, kStatic>;
   constexpr uint32_t smem = smem_bytes_for(TOK);
   static bool configured[64] = {false};
   int dev = 0;
@@ -1053,6 +1123,12 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
     if (pick_splits(tok_tile, tiles, static_cast<int>((a.K + kBlockK - 1) / kBlockK), sm_count(), a.split_workspace_bytes) >= 2)
       return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, false, true>(a, tok_tile, stream)
                   : launch_variant<128, kGroup, true, false, __half, false, false, false, true>(a, tok_tile, stream);
+  }
+  if (TOK == 128 && kGroup && eo && !dump && ((a.K / kBlockK) & 7) == 0 && (a.K % kBlockK) == 0 &&
+      (reinterpret_cast<uintptr_t>(a.w_scales) & 15u) == 0) {
+    // whole chunks of eight group scales per tile, no K split: the variant with the ring position unrolled
+    return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, false, false, kGroup>(a, tok_tile, stream)
+                : launch_variant<128, kGroup, true, false, __half, false, false, false, false, kGroup>(a, tok_tile, stream);
   }
   if (eo) return dump ? SQ_LAUNCH(true, true) : SQ_LAUNCH(true, false);
   return dump ? SQ_LAUNCH(false, true) : SQ_LAUNCH(false, false);
