@@ -179,34 +179,33 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
   atomicCAS(status, 0, code);
 }
 
-// One group of the drain (group form, chunked scales, no K split) with the accumulator ring position POS a
-// compile-time constant: barrier addresses, TMEM columns and the ring's phase then cost no instructions.  `g` is the
-// group index of position 0 of the round (a multiple of four).  Returns false when the wait gave up.
-template <uint32_t POS, int kCols>
+// One group of the drain (group form, chunked scales, no K split) with its place E in the chunk of eight group
+// scales - and with it its place E mod 4 in the accumulator ring - a compile-time constant: barrier addresses, TMEM
+// columns, the ring's phase and the position of the scale inside the chunk then cost no instructions.  `g` is the
+// group index of place 0 of the round (a multiple of eight), `phase` the ring's parity at place 0 (the same at place
+// 4: two ring rounds per chunk, so it flips there).  Returns false when the wait gave up.
+template <uint32_t E, int kCols>
 __device__ __forceinline__ bool drain_group_static(uint32_t bar_acc_full, uint32_t bar_acc_empty, uint32_t tmem_slice,
                                                    uint32_t phase, volatile int* abort_flag, int lane,
                                                    bool& acc_ready, uint4& chunk, uint4& chunk_next,
                                                    const unsigned short* my_scales, int groups, int g,
                                                    float offset_float, float& offset_sum, uint64_t (&sums2)[kCols / 2]) {
-  if (!acc_ready && !mbar_wait_bounded(bar_acc_full + 8 * POS, phase, abort_flag, 1000ull * 1000ull * 1000ull)) return false;
+  constexpr uint32_t POS = E & 3u;
+  const uint32_t my_phase = E < 4u ? phase : phase ^ 1u;
+  if (!acc_ready && !mbar_wait_bounded(bar_acc_full + 8 * POS, my_phase, abort_flag, 1000ull * 1000ull * 1000ull)) return false;
   tc_fence_after_sync();
   uint32_t r[kCols];
   tmem_ld_chunk(tmem_slice + POS * 128u, r);
   // the next group's barrier is probed under the load (a probe takes over a hundred cycles to answer)
-  acc_ready = mbar_test_wait(bar_acc_full + 8 * ((POS + 1u) & 3u), POS == 3u ? phase ^ 1u : phase);
-  // the lowest half of the chunk is this group's scale; the chunk then moves down by one half
-  const unsigned short raw = static_cast<unsigned short>(chunk.x & 0xFFFFu);
-  if (POS == 3u && (g & 4) != 0) {  // group g + 3 was the last of its chunk
+  acc_ready = mbar_test_wait(bar_acc_full + 8 * ((POS + 1u) & 3u), POS == 3u ? my_phase ^ 1u : my_phase);
+  const uint32_t word = E < 2u ? chunk.x : E < 4u ? chunk.y : E < 6u ? chunk.z : chunk.w;
+  const __half2 pair = *reinterpret_cast<const __half2*>(&word);
+  const float scale = ((E & 1u) != 0u ? __high2float(pair) : __low2float(pair)) * 7.922816251426434e28f;  // 2^96 (kScaleUp)
+  if (E == 7u) {  // the chunk is used up: the next one takes its place, the one after that is requested
     chunk = chunk_next;
-    const int c2 = ((g + 3) >> 3) + 2;
+    const int c2 = (g >> 3) + 2;
     if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
-  } else {
-    chunk.x = __funnelshift_r(chunk.x, chunk.y, 16);
-    chunk.y = __funnelshift_r(chunk.y, chunk.z, 16);
-    chunk.z = __funnelshift_r(chunk.z, chunk.w, 16);
-    chunk.w >>= 16;
   }
-  const float scale = __half2float(__ushort_as_half(raw)) * 7.922816251426434e28f;  // 2^96 (kScaleUp)
   offset_sum = fmaf(offset_float, scale, offset_sum);
   tmem_wait_ld();
   tc_fence_before_sync();
@@ -597,22 +596,20 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 
       if constexpr (kStatic) {
         // The launcher picks this variant when every tile has a multiple of eight groups in chunked scales and K is
-        // not split: four groups per round, each with its place in the accumulator ring a compile-time constant.
+        // not split: eight groups (one chunk of scales) per round, each with its place in the chunk and in the
+        // accumulator ring a compile-time constant.
         // The instructions a drain warp spends per group are what bounds this kernel.
         if (my_cols > 0) {
-          uint32_t phase = (git >> 2) & 1u;
+          const uint32_t phase = (git >> 2) & 1u;  // git is a multiple of eight at every round: the same parity each time
           const uint32_t tmem_slice = tmem_base + lane_addr + my_col0;
-          for (int g = g0; g < g1 && ok; g += 4, git += 4) {
-            ok = drain_group_static<0u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
-                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2) &&
-                 drain_group_static<1u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
-                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2) &&
-                 drain_group_static<2u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
-                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2) &&
-                 drain_group_static<3u, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready,
-                                               chunk, chunk_next, my_scales, groups, g, offset_float, offset_sum, sums2);
-            phase ^= 1u;
+#define SQ_DRAIN_AT(E)                                                                                                   \
+  drain_group_static<E, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready, chunk, chunk_next, \
+                               my_scales, groups, g, offset_float, offset_sum, sums2)
+          for (int g = g0; g < g1 && ok; g += 8, git += 8) {
+            ok = SQ_DRAIN_AT(0u) && SQ_DRAIN_AT(1u) && SQ_DRAIN_AT(2u) && SQ_DRAIN_AT(3u) && SQ_DRAIN_AT(4u) &&
+                 SQ_DRAIN_AT(5u) && SQ_DRAIN_AT(6u) && SQ_DRAIN_AT(7u);
           }
+#undef SQ_DRAIN_AT
         } else {
           // a warp whose columns lie beyond the tile's tokens only keeps the accumulator hand-over going
           for (int g = g0; g < g1 && ok; ++g, ++git) {
@@ -1112,6 +1109,12 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
     return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, true>(a, tok_tile, stream)
                 : launch_variant<128, kGroup, true, false, __half, false, false, true>(a, tok_tile, stream);
   }
+  const bool whole_chunks = TOK == 128 && kGroup && eo && !dump && ((a.K / kBlockK) & 7) == 0 && (a.K % kBlockK) == 0 &&
+                            (reinterpret_cast<uintptr_t>(a.w_scales) & 15u) == 0;
+  if (a.weights_prepacked && whole_chunks) {
+    return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, true, false, false, kGroup>(a, tok_tile, stream)
+                : launch_variant<128, kGroup, true, false, __half, false, true, false, false, kGroup>(a, tok_tile, stream);
+  }
   if (a.weights_prepacked) {  // validated: even-odd codes, no accumulator dump
     return bf16 ? launch_variant<TOK, kGroup, true, false, __nv_bfloat16, false, true>(a, tok_tile, stream)
                 : launch_variant<TOK, kGroup, true, false, __half, false, true>(a, tok_tile, stream);
@@ -1124,8 +1127,7 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
       return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, false, true>(a, tok_tile, stream)
                   : launch_variant<128, kGroup, true, false, __half, false, false, false, true>(a, tok_tile, stream);
   }
-  if (TOK == 128 && kGroup && eo && !dump && ((a.K / kBlockK) & 7) == 0 && (a.K % kBlockK) == 0 &&
-      (reinterpret_cast<uintptr_t>(a.w_scales) & 15u) == 0) {
+  if (whole_chunks) {
     // whole chunks of eight group scales per tile, no K split: the variant with the ring position unrolled
     return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, false, false, kGroup>(a, tok_tile, stream)
                 : launch_variant<128, kGroup, true, false, __half, false, false, false, false, kGroup>(a, tok_tile, stream);
