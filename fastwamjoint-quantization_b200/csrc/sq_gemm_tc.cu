@@ -335,6 +335,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     if (warp == 0) {
       // TMA producer
       uint32_t it = 0;
+      uint32_t s = 0, phase = 0;  // stage of the ring and its phase, as running values
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         int tile, kb0, kb1;
@@ -342,7 +343,6 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const int ch0 = (tile % p.ch_tiles) * kBlockCh;
         const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const uint32_t s = it % S, phase = (it / S) & 1u;
           if (!mbar_wait_bounded(bar_empty + 8 * s, phase ^ 1u, abort_flag, kWaitLimitNs)) {
             if (lane == 0) report_timeout(p.status, abort_flag, 9001);
             ok = false;
@@ -366,6 +366,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             }
           }
           __syncwarp();
+          if (++s == S) {
+            s = 0;
+            phase ^= 1u;
+          }
         }
       }
     } else if (warp <= kMmaWarps) {
@@ -452,13 +456,21 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     reg_dec<regs_unpack(kWideDrain)>();
     const int ctid = threadIdx.x - 128;  // 0..127
     uint32_t it = 0;
+    // stage of the ring and its phase, kept as running values (a division by the stage count per block is a
+    // dozen instructions on a warp whose time per block bounds the packed form)
+    uint32_t s = 0, phase = 0;
     bool ok = true;
     bool stage_ready = false;  // an early probe saw the coming stage's packed weights landed
+    // what does not change from block to block: this thread's 16-byte units of the packed tile and where their
+    // unpacked halves go inside the swizzled operand tile (the swizzle only looks at the row's low bits)
+    const uint32_t src_off = static_cast<uint32_t>(ctid) * 16u;
+    const uint32_t row0 = static_cast<uint32_t>(ctid >> 2), c0 = static_cast<uint32_t>(ctid & 3);
+    const uint32_t dst_off_a = row0 * 128u + (((2u * c0) ^ (row0 & 7u)) << 4);
+    const uint32_t dst_off_b = row0 * 128u + (((2u * c0 + 1u) ^ (row0 & 7u)) << 4);
     for (int item = blockIdx.x; !kPre && item < num_items && ok; item += gridDim.x) {
       int tile, kb0, kb1;
       item_range(item, tile, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const uint32_t s = it % S, phase = (it / S) & 1u;
         if (!(SQ_TC_EARLY_PROBE && stage_ready) && !mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9004);
           ok = false;
@@ -471,17 +483,16 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         uint32_t win[4][4];
 #pragma unroll
         for (int u4 = 0; u4 < 4; ++u4) {
-          const int unit = u4 * 128 + ctid;  // 16 packed bytes = 32 k of one channel row
+          // unit u4 * 128 + ctid: 16 packed bytes = 32 k of one channel row
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(win[u4][0]), "=r"(win[u4][1]), "=r"(win[u4][2]), "=r"(win[u4][3])
-                       : "r"(src + unit * 16));
+                       : "r"(src + src_off + u4 * 2048));
         }
         // the next stage's barrier is probed under this stage's work (a probe takes over a hundred cycles)
-        if (SQ_TC_EARLY_PROBE) stage_ready = mbar_test_wait(bar_full + 8 * ((it + 1) % S), (((it + 1) / S) & 1u));
+        const uint32_t s_next = s + 1 == S ? 0u : s + 1, phase_next = s + 1 == S ? phase ^ 1u : phase;
+        if (SQ_TC_EARLY_PROBE) stage_ready = mbar_test_wait(bar_full + 8 * s_next, phase_next);
 #pragma unroll
         for (int u4 = 0; u4 < 4; ++u4) {
-          const int unit = u4 * 128 + ctid;
-          const int row = unit >> 2, c = unit & 3;
           uint32_t o[8];
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -495,17 +506,18 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               o[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // k4 k5 k6 k7
             }
           }
-          const uint32_t row_base = dst + row * 128;
-          const uint32_t sw = static_cast<uint32_t>(row & 7);
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (((2 * c) ^ sw) << 4)),
+          // row u4 * 32 + ctid / 4: 32 rows = 4 KiB further on per unit, the same place inside the swizzle atom
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + dst_off_a + u4 * 4096),
                        "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]));
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row_base + (((2 * c + 1) ^ sw) << 4)),
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + dst_off_b + u4 * 4096),
                        "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
         }
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_wfull + 8 * s);
         if (ctid == 0) stamp(kTrConvDone, it);
+        s = s_next;
+        phase = phase_next;
       }
     }
   } else {
