@@ -45,19 +45,22 @@ namespace {
 constexpr int kBlockCh = 128;  // output channels per tile = UMMA M = TMEM lanes
 constexpr int kBlockK = 128;   // int8 K elements per stage = one swizzle row = one weight group
 constexpr int kUmmaK = 32;     // K of one kind::i8 instruction
-constexpr int kThreads = 768;  // 4 control + 4 unpack + 16 drain warps
 // Register targets per role after setmaxnreg (control 24, unpack 40, drain 104).  setmaxnreg.inc only hands out
 // registers the CTA was launched with and waits for ever when the targets add up to more, so the launcher
 // checks this sum against (registers per thread at launch) x kThreads before every launch.
 // Registers per thread after the roles re-partition the CTA's allocation (setmaxnreg).  `wide_drain`: the variant of
 // the 128-token kernel that can split K keeps a few more values live in its drain loop and takes the registers for
 // them from the other roles.
-__host__ __device__ constexpr int regs_control(bool wide_drain) { return wide_drain ? 24 : 32; }
-__host__ __device__ constexpr int regs_unpack(bool wide_drain) { return wide_drain ? 40 : 48; }
-__host__ __device__ constexpr int regs_drain(bool wide_drain) { return wide_drain ? 104 : 96; }
-__host__ __device__ constexpr int register_pool_needed(bool wide_drain) {
-  return 4 * 32 * regs_control(wide_drain) + 4 * 32 * regs_unpack(wide_drain) + 16 * 32 * regs_drain(wide_drain);
+// `dw`: drain warps per TMEM lane quarter.  Four warps of 32 token columns each (768 threads, 80 registers per thread
+// at launch), or two of 64 columns (512 threads, 128 registers at launch: a drain warp then holds 64 sums and the 64
+// accumulator words of a group).
+__host__ __device__ constexpr int regs_control(bool wide_drain, int dw = 4) { return dw == 2 ? 32 : wide_drain ? 24 : 32; }
+__host__ __device__ constexpr int regs_unpack(bool wide_drain, int dw = 4) { return dw == 2 ? 48 : wide_drain ? 40 : 48; }
+__host__ __device__ constexpr int regs_drain(bool wide_drain, int dw = 4) { return dw == 2 ? 216 : wide_drain ? 104 : 96; }
+__host__ __device__ constexpr int register_pool_needed(bool wide_drain, int dw = 4) {
+  return 4 * 32 * regs_control(wide_drain, dw) + 4 * 32 * regs_unpack(wide_drain, dw) + 4 * dw * 32 * regs_drain(wide_drain, dw);
 }
+__host__ __device__ constexpr int threads_for(int dw) { return 256 + 128 * dw; }  // 4 control + 4 unpack + 4 dw drain warps
 constexpr uint32_t kPackedBytes = kBlockCh * kBlockK / 2;  // 8 KiB
 constexpr uint32_t kWBytes = kBlockCh * kBlockK;           // 16 KiB
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
@@ -80,7 +83,6 @@ constexpr float kScaleUp = 7.922816251426434e28f;    // 2^96: keeps acc * 2^-149
 constexpr float kScaleDown = 562949953421312.0f;     // 2^49 = 2^149 / 2^96 / 16 (the unpacked weights are 16 w)
 
 constexpr int kNumConverterWarps = 4;
-constexpr int kNumDrainWarps = 16;  // four per TMEM lane quarter, each owns a slice of the token columns
 
 #ifndef SQ_TC_STAGES128
 #define SQ_TC_STAGES128 5
@@ -217,6 +219,74 @@ __device__ __forceinline__ bool drain_group_static(uint32_t bar_acc_full, uint32
   return true;
 }
 
+// The finished sums of a tile that wait for their finalize (two-warp drain): columns [kFirst, kFirst + kCount) of a
+// drain warp's 64 get their row scale (by shuffle from the lane that fetched it), bias and cast, and are stored.
+// `cols`: how many of the warp's columns are real tokens (0: nothing is pending, or this lane's channel does not exist);
+// the shuffles run in every lane.  The arithmetic is the finalize of the four-warp drain, operation for operation.
+template <typename OutT>
+struct PendingTile {
+  uint64_t sums2[32];
+  float offset_sum;
+  float rs[2];
+  float bias;
+  OutT* out;  // row of the slice's first token, this lane's channel
+  int cols;
+};
+template <int kFirst, int kCount, typename OutT>
+__device__ __forceinline__ void finalize_pending(const PendingTile<OutT>& t, bool has_bias, int64_t out_ld) {
+#pragma unroll
+  for (int i = kFirst; i < kFirst + kCount; ++i) {
+    const float rs = __shfl_sync(0xffffffffu, t.rs[i >> 5], i & 31);
+    const float2 pair = unpack2(t.sums2[i / 2]);
+    float y = __fmul_rn(__fsub_rn((i & 1) != 0 ? pair.y : pair.x, t.offset_sum), rs);
+    if (has_bias) y = __fadd_rn(y, t.bias);
+    if (i < t.cols) t.out[i * out_ld] = from_float<OutT>(y);
+  }
+}
+
+// A group of a tile's first round in the two-warp drain: as drain_group_static, but the 64 columns come as two loads
+// of 32 (the registers of a full-width load are taken by the pending sums), and eight columns of the pending tile
+// are finalized while those loads are in flight: the finalize of tile t runs under the first eight groups of tile
+// t + 1 instead of holding up the accumulator ring between the tiles.
+template <uint32_t E, typename OutT>
+__device__ __forceinline__ bool drain_group_first(uint32_t bar_acc_full, uint32_t bar_acc_empty, uint32_t tmem_slice,
+                                                  uint32_t phase, volatile int* abort_flag, int lane, bool& acc_ready,
+                                                  uint4& chunk, uint4& chunk_next, const unsigned short* my_scales,
+                                                  int groups, int g, float offset_float, float& offset_sum,
+                                                  uint64_t (&sums2)[32], const PendingTile<OutT>& pending, bool has_bias,
+                                                  int64_t out_ld) {
+  constexpr uint32_t POS = E & 3u;
+  const uint32_t my_phase = E < 4u ? phase : phase ^ 1u;
+  if (!acc_ready && !mbar_wait_bounded(bar_acc_full + 8 * POS, my_phase, abort_flag, 1000ull * 1000ull * 1000ull)) return false;
+  tc_fence_after_sync();
+  uint32_t r[32];
+  tmem_ld_chunk(tmem_slice + POS * 128u, r);
+  acc_ready = mbar_test_wait(bar_acc_full + 8 * ((POS + 1u) & 3u), POS == 3u ? my_phase ^ 1u : my_phase);
+  const uint32_t word = E < 2u ? chunk.x : E < 4u ? chunk.y : E < 6u ? chunk.z : chunk.w;
+  const __half2 pair = *reinterpret_cast<const __half2*>(&word);
+  const float scale = ((E & 1u) != 0u ? __high2float(pair) : __low2float(pair)) * 7.922816251426434e28f;  // 2^96 (kScaleUp)
+  if (E == 7u) {
+    chunk = chunk_next;
+    const int c2 = (g >> 3) + 2;
+    if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+  }
+  offset_sum = fmaf(offset_float, scale, offset_sum);
+  const uint64_t scale2 = pack2(scale, scale);
+  finalize_pending<8 * E, 4, OutT>(pending, has_bias, out_ld);
+  tmem_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) ffma2(sums2[i / 2], r[i], r[i + 1], scale2);
+  tmem_ld_chunk(tmem_slice + POS * 128u + 32u, r);
+  finalize_pending<8 * E + 4, 4, OutT>(pending, has_bias, out_ld);
+  tmem_wait_ld();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_acc_empty + 8 * POS);
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) ffma2(sums2[16 + i / 2], r[i], r[i + 1], scale2);
+  return true;
+}
+
 // TOK    capacity in tokens of one tile (TMEM columns per accumulator, rows of a codes stage); the
 //        tile actually used, p.tok_tile <= TOK, is chosen per call so the tiles fill the SMs evenly
 // kGroup one accumulator per 128-K weight group (fp16 scales [N, K/128]); otherwise one per tile (fp32 [N])
@@ -225,8 +295,8 @@ __device__ __forceinline__ bool drain_group_static(uint32_t bar_acc_full, uint32
 // kPre   the weights arrive already unpacked (int8 = 16 w, even-odd k order, from sq_prepack_weights): TMA puts
 //        them straight into the operand tile and the unpack warps have nothing to do
 template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
-          bool kScatter = false, bool kSplit = (TOK <= 64), bool kStatic = false>
-__global__ void __launch_bounds__(kThreads, 1)
+          bool kScatter = false, bool kSplit = (TOK <= 64), bool kStatic = false, int kDW = 4>
+__global__ void __launch_bounds__(threads_for(kDW), 1)
 sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_packed,
                   const TcParams p) {
   constexpr int S = stages_for(TOK);
@@ -235,7 +305,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   // reads them with ONE tcgen05.ld (a TMEM load costs a few hundred cycles whatever its width, and the
   // loads of one warp do not overlap each other).  While some warps of a scheduler wait for their load,
   // the others convert and accumulate: four warps per scheduler hide the TMEM and barrier round trips.
-  constexpr int kCols = TOK / 4 < 16 ? 16 : TOK / 4;  // 32 or 16 columns per drain warp
+  constexpr int kCols = TOK / kDW < 16 ? 16 : TOK / kDW;  // 64, 32 or 16 columns per drain warp
+  static_assert(kDW == 4 || (kDW == 2 && TOK == 128 && kStatic && !kSplit && !kScatter), "the two-warp drain serves the static form only");
   // TMEM holds a ring of four accumulators so the MMA warp can run ahead of the drain by three groups
   constexpr uint32_t kAccBufs = 4;
   // Channel form: two issuers take alternate K blocks into private accumulators (buffers 2j, 2j + 1 of tile
@@ -244,6 +315,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   constexpr int kMmaWarps = kGroup ? 3 : 2;
   constexpr uint32_t kBufStride = 128;  // TMEM columns between accumulators
   constexpr uint32_t kTmemCols = 512;
+  // Two-warp drain: the unpack warps work in pairs on alternate K blocks (each pair the whole block) instead of all
+  // four on every block: a warp's chain per block (barrier, loads, unpack, stores, proxy fence, arrive) then has two
+  // block times to finish in.
+  constexpr bool kUnpackPairs = kDW == 2 && !kPre;
   static_assert(TOK == 128 || TOK == 64 || TOK == 32, "tile capacities");
 
   extern __shared__ uint8_t smem_raw[];
@@ -270,12 +345,12 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_wfull + 8 * s, kPre ? 1 : kNumConverterWarps);
+      mbar_init(bar_wfull + 8 * s, kPre ? 1 : kUnpackPairs ? kNumConverterWarps / 2 : kNumConverterWarps);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < static_cast<int>(kAccBufs); ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
-      mbar_init(bar_acc_empty + 8 * b, kNumDrainWarps);
+      mbar_init(bar_acc_empty + 8 * b, 4 * kDW);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -288,7 +363,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
   }
   if (kGroup) {
     uint32_t* c_words = reinterpret_cast<uint32_t*>(smem_gen + (c_tile - smem_base));
-    for (uint32_t i = threadIdx.x; i < kConstTileBytes / 4; i += kThreads) c_words[i] = p.offset_word;
+    for (uint32_t i = threadIdx.x; i < kConstTileBytes / 4; i += blockDim.x) c_words[i] = p.offset_word;
     fence_proxy_async_smem();  // the tensor core reads this tile through the async proxy
   }
   tc_fence_before_sync();
@@ -328,7 +403,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 
   if (warp < 4) {
     // ------------------------------------------------------------------ control warpgroup
-    reg_dec<regs_control(kWideDrain)>();
+    reg_dec<regs_control(kWideDrain, kDW)>();
     // Both roles keep the whole warp in the loop and pick the issuing thread with elect.sync: TMA and
     // tcgen05 instructions take warp-uniform operands, and only an elected region lets the compiler keep
     // them in uniform registers (a plain `lane == 0` branch costs about a hundred cycles per instruction).
@@ -453,12 +528,16 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ converter warpgroup
-    reg_dec<regs_unpack(kWideDrain)>();
-    const int ctid = threadIdx.x - 128;  // 0..127
+    reg_dec<regs_unpack(kWideDrain, kDW)>();
+    // kUnpackPairs: 64 threads per K block, eight 16-byte units each; otherwise 128 threads, four units each
+    constexpr int kUnits = kUnpackPairs ? 8 : 4;
+    constexpr uint32_t kStep = kUnpackPairs ? 2u : 1u;           // K blocks between two blocks of this warp
+    const int ctid = kUnpackPairs ? (threadIdx.x - 128) & 63 : threadIdx.x - 128;
+    const uint32_t pair = kUnpackPairs ? static_cast<uint32_t>(threadIdx.x - 128) >> 6 : 0u;
     uint32_t it = 0;
     // stage of the ring and its phase, kept as running values (a division by the stage count per block is a
     // dozen instructions on a warp whose time per block bounds the packed form)
-    uint32_t s = 0, phase = 0;
+    uint32_t s = pair, phase = 0;
     bool ok = true;
     bool stage_ready = false;  // an early probe saw the coming stage's packed weights landed
     // what does not change from block to block: this thread's 16-byte units of the packed tile and where their
@@ -467,10 +546,13 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     const uint32_t row0 = static_cast<uint32_t>(ctid >> 2), c0 = static_cast<uint32_t>(ctid & 3);
     const uint32_t dst_off_a = row0 * 128u + (((2u * c0) ^ (row0 & 7u)) << 4);
     const uint32_t dst_off_b = row0 * 128u + (((2u * c0 + 1u) ^ (row0 & 7u)) << 4);
+    constexpr uint32_t kSrcStride = kUnpackPairs ? 1024u : 2048u;  // between a thread's units: 64 or 128 units on
+    constexpr uint32_t kDstStride = kUnpackPairs ? 2048u : 4096u;  // 16 or 32 rows on
     for (int item = blockIdx.x; !kPre && item < num_items && ok; item += gridDim.x) {
       int tile, kb0, kb1;
       item_range(item, tile, kb0, kb1);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        if (kUnpackPairs && (it & 1u) != pair) continue;  // the other pair's block
         if (!(SQ_TC_EARLY_PROBE && stage_ready) && !mbar_wait_bounded(bar_full + 8 * s, phase, abort_flag, kWaitLimitNs)) {
           if (lane == 0) report_timeout(p.status, abort_flag, 9004);
           ok = false;
@@ -479,38 +561,41 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         if (ctid == 0) stamp(kTrConvStart, it);
         const uint32_t src = p_ring + s * kPackedBytes;
         const uint32_t dst = w_ring + s * kWBytes;
-        // all four 16-byte loads first, then the unpack and the eight stores: the loads overlap
-        uint32_t win[4][4];
+        const uint32_t s_next = s + kStep >= S ? s + kStep - S : s + kStep, phase_next = s + kStep >= S ? phase ^ 1u : phase;
 #pragma unroll
-        for (int u4 = 0; u4 < 4; ++u4) {
-          // unit u4 * 128 + ctid: 16 packed bytes = 32 k of one channel row
-          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(win[u4][0]), "=r"(win[u4][1]), "=r"(win[u4][2]), "=r"(win[u4][3])
-                       : "r"(src + src_off + u4 * 2048));
-        }
-        // the next stage's barrier is probed under this stage's work (a probe takes over a hundred cycles)
-        const uint32_t s_next = s + 1 == S ? 0u : s + 1, phase_next = s + 1 == S ? phase ^ 1u : phase;
-        if (SQ_TC_EARLY_PROBE) stage_ready = mbar_test_wait(bar_full + 8 * s_next, phase_next);
+        for (int half = 0; half < kUnits / 4; ++half) {
+          // four 16-byte loads first, then the unpack and the eight stores: the loads overlap
+          uint32_t win[4][4];
 #pragma unroll
-        for (int u4 = 0; u4 < 4; ++u4) {
-          uint32_t o[8];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint32_t lo = (win[u4][i] << 4) & 0xF0F0F0F0u;  // 16 * nibble of even k, as int8
-            const uint32_t hi = win[u4][i] & 0xF0F0F0F0u;         // 16 * nibble of odd k
-            if (kEvenOdd) {
-              o[2 * i] = lo;
-              o[2 * i + 1] = hi;
-            } else {
-              o[2 * i] = __byte_perm(lo, hi, 0x5140);      // k0 k1 k2 k3
-              o[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // k4 k5 k6 k7
-            }
+          for (int u4 = 0; u4 < 4; ++u4) {
+            // unit (4 half + u4) * threads + ctid: 16 packed bytes = 32 k of one channel row
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(win[u4][0]), "=r"(win[u4][1]), "=r"(win[u4][2]), "=r"(win[u4][3])
+                         : "r"(src + src_off + (4 * half + u4) * kSrcStride));
           }
-          // row u4 * 32 + ctid / 4: 32 rows = 4 KiB further on per unit, the same place inside the swizzle atom
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + dst_off_a + u4 * 4096),
-                       "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]));
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + dst_off_b + u4 * 4096),
-                       "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
+          // the next stage's barrier is probed under this stage's work (a probe takes over a hundred cycles)
+          if (SQ_TC_EARLY_PROBE && half == 0) stage_ready = mbar_test_wait(bar_full + 8 * s_next, phase_next);
+#pragma unroll
+          for (int u4 = 0; u4 < 4; ++u4) {
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t lo = (win[u4][i] << 4) & 0xF0F0F0F0u;  // 16 * nibble of even k, as int8
+              const uint32_t hi = win[u4][i] & 0xF0F0F0F0u;         // 16 * nibble of odd k
+              if (kEvenOdd) {
+                o[2 * i] = lo;
+                o[2 * i + 1] = hi;
+              } else {
+                o[2 * i] = __byte_perm(lo, hi, 0x5140);      // k0 k1 k2 k3
+                o[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // k4 k5 k6 k7
+              }
+            }
+            // the same place inside the swizzle atom, kDstStride further on per unit
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + dst_off_a + (4 * half + u4) * kDstStride),
+                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]));
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + dst_off_b + (4 * half + u4) * kDstStride),
+                         "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]));
+          }
         }
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's async proxy
         __syncwarp();
@@ -522,10 +607,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ drain warpgroups
-    reg_inc<regs_drain(kWideDrain)>();
-    const int dwarp = warp - 8;           // 0..15
+    reg_inc<regs_drain(kWideDrain, kDW)>();
+    const int dwarp = warp - 8;           // 0..4 kDW - 1
     const int quarter = warp & 3;         // TMEM lane quarter this warp may address
-    const int slice = dwarp >> 2;         // which slice of the token columns (four warps per lane quarter)
+    const int slice = dwarp >> 2;         // which slice of the token columns (kDW warps per lane quarter)
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int ch_in_tile = quarter * 32 + lane;
 
@@ -544,6 +629,15 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     uint32_t git = 0;
     bool ok = true;
     bool acc_ready = false;  // an early probe saw the coming group's accumulator complete
+    // two-warp drain: the sums of the tile before, finalized under the first groups of the tile in hand
+    PendingTile<OutT> pending;
+    pending.cols = 0;
+    pending.offset_sum = 0.0f;
+    pending.rs[0] = pending.rs[1] = 0.0f;
+    pending.bias = 0.0f;
+    pending.out = static_cast<OutT*>(p.out);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) pending.sums2[i] = 0ull;
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       int tile, kb0, kb1;
       item_range(item, tile, kb0, kb1);
@@ -561,8 +655,12 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       float* part_out = kSplitK && splits > 1
                             ? p.partials + (static_cast<int64_t>(item) * p.tok_tile + my_col0) * kBlockCh + ch_in_tile
                             : nullptr;
-      float my_rs = lane < my_cols ? __ldg(p.row_scales + m0 + lane) : 0.0f;
-      if (kGroup) my_rs = __fmul_rn(my_rs, kScaleDown);
+      float my_rs[kCols > 32 ? 2 : 1];
+#pragma unroll
+      for (int h = 0; h < (kCols > 32 ? 2 : 1); ++h) {
+        my_rs[h] = 32 * h + lane < my_cols ? __ldg(p.row_scales + m0 + 32 * h + lane) : 0.0f;
+        if (kGroup) my_rs[h] = __fmul_rn(my_rs[h], kScaleDown);
+      }
       const bool has_bias = p.bias != nullptr;
       const float bias = has_bias && n_ok ? to_float<OutT>(__ldg(static_cast<const OutT*>(p.bias) + n)) : 0.0f;
       const float wscale = !kGroup && n_ok ? __ldg(static_cast<const float*>(p.w_scales) + n) : 1.0f;
@@ -606,7 +704,54 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         }
       }
 
-      if constexpr (kStatic) {
+      if constexpr (kStatic && kDW == 2) {
+        const bool has_bias_now = p.bias != nullptr;
+        if (my_cols > 0) {
+          const uint32_t phase = (git >> 2) & 1u;
+          const uint32_t tmem_slice = tmem_base + lane_addr + my_col0;
+          int g = g0;
+#define SQ_DRAIN_FIRST(E)                                                                                               \
+  drain_group_first<E, OutT>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready, chunk, chunk_next, \
+                             my_scales, groups, g, offset_float, offset_sum, sums2, pending, has_bias_now, p.out_ld)
+#define SQ_DRAIN_AT(E)                                                                                                   \
+  drain_group_static<E, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready, chunk, chunk_next, \
+                               my_scales, groups, g, offset_float, offset_sum, sums2)
+          ok = SQ_DRAIN_FIRST(0u) && SQ_DRAIN_FIRST(1u) && SQ_DRAIN_FIRST(2u) && SQ_DRAIN_FIRST(3u) && SQ_DRAIN_FIRST(4u) &&
+               SQ_DRAIN_FIRST(5u) && SQ_DRAIN_FIRST(6u) && SQ_DRAIN_FIRST(7u);
+          git += 8;
+          for (g = g0 + 8; g < g1 && ok; g += 8, git += 8) {
+            ok = SQ_DRAIN_AT(0u) && SQ_DRAIN_AT(1u) && SQ_DRAIN_AT(2u) && SQ_DRAIN_AT(3u) && SQ_DRAIN_AT(4u) &&
+                 SQ_DRAIN_AT(5u) && SQ_DRAIN_AT(6u) && SQ_DRAIN_AT(7u);
+          }
+#undef SQ_DRAIN_AT
+#undef SQ_DRAIN_FIRST
+        } else {
+          // no columns of this tile (past the last token): finalize what is pending, keep the hand-over going
+          finalize_pending<0, 64, OutT>(pending, has_bias_now, p.out_ld);
+          for (int g = g0; g < g1 && ok; ++g, ++git) {
+            const uint32_t buf = git & 3u;
+            ok = mbar_wait_bounded(bar_acc_full + 8 * buf, (git >> 2) & 1u, abort_flag, kWaitLimitNs);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+          }
+          acc_ready = false;
+        }
+        if (!ok) {
+          if (lane == 0) report_timeout(p.status, abort_flag, 9005);
+          break;
+        }
+        // this tile's sums now wait for their turn
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pending.sums2[i] = sums2[i];
+        pending.offset_sum = offset_sum;
+        pending.rs[0] = my_rs[0];
+        pending.rs[1] = my_rs[kCols > 32 ? 1 : 0];
+        pending.bias = bias;
+        pending.out = static_cast<OutT*>(p.out) + m0 * p.out_ld + p.out_col0 + (n_ok ? n : 0);
+        pending.cols = n_ok ? my_cols : 0;
+        continue;
+      } else if constexpr (kStatic) {
         // The launcher picks this variant when every tile has a multiple of eight groups in chunked scales and K is
         // not split: eight groups (one chunk of scales) per round, each with its place in the chunk and in the
         // accumulator ring a compile-time constant.
@@ -635,7 +780,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         }
         if (!ok && lane == 0) report_timeout(p.status, abort_flag, 9005);
       }
-      for (int g = g0; !kStatic && g < g1 && ok; ++g, ++git) {
+      if constexpr (!kStatic)
+      for (int g = g0; g < g1 && ok; ++g, ++git) {
         // channel form: the tile's accumulator pair (2j, 2j + 1), the second in use when the issuers split K
         const uint32_t buf = kGroup ? git % kAccBufs : (git & 1u) * 2u;
         const uint32_t aphase = kGroup ? (git / kAccBufs) & 1u : (git >> 1) & 1u;
@@ -855,7 +1001,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         // the common case is kept apart from the fused forms: a short straight run of instructions per column
 #pragma unroll
         for (int i = 0; i < kCols; ++i) {
-          const float rs = __shfl_sync(0xffffffffu, my_rs, i);
+          const float rs = __shfl_sync(0xffffffffu, my_rs[i >> 5], i & 31);
           float y;
           if (kGroup) {
             const float2 pair = unpack2(sums2[kGroup ? i / 2 : 0]);
@@ -882,7 +1028,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         const OutT* residual = p.residual != nullptr ? static_cast<const OutT*>(p.residual) + m0 * p.N + (n_ok ? n : 0) : nullptr;
 #pragma unroll
         for (int i = 0; i < kCols; ++i) {
-          const float rs = __shfl_sync(0xffffffffu, my_rs, i);
+          const float rs = __shfl_sync(0xffffffffu, my_rs[i >> 5], i & 31);
           float y;
           if (kGroup) {
             const float2 pair = unpack2(sums2[kGroup ? i / 2 : 0]);
@@ -906,6 +1052,9 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         }
       }
       if (threadIdx.x == 256) stamp(kTrTileEnds, 2 * (git / groups) - 1);
+    }
+    if constexpr (kStatic && kDW == 2) {
+      if (ok) finalize_pending<0, 64, OutT>(pending, p.bias != nullptr, p.out_ld);
     }
   }
 
@@ -1002,9 +1151,10 @@ int pick_tok_tile(int64_t M, int ch_tiles, int k_blocks, int sms, size_t split_b
 }
 
 template <int TOK, bool kGroup, bool kEvenOdd, bool kDump, typename OutT, bool kTrace = false, bool kPre = false,
-          bool kScatter = false, bool kSplit = (TOK <= 64), bool kStatic = false>
+          bool kScatter = false, bool kSplit = (TOK <= 64), bool kStatic = false, int kDW = 4>
 int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long long* timeline = nullptr) {
-  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre, kScatter, kSplit, kStatic>;
+  auto kernel = sq_gemm_tc_kernel<TOK, kGroup, kEvenOdd, kDump, OutT, kTrace, kPre, kScatter, kSplit, kStatic, kDW>;
+  constexpr int kThreads = threads_for(kDW);
   constexpr uint32_t smem = smem_bytes_for(TOK);
   static bool configured[64] = {false};
   int dev = 0;
@@ -1033,9 +1183,9 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
   p.tok_tile = tok_tile;
-  {  // a quarter of the tile rounded up to 16 columns, at most a drain warp's register capacity
-    const int cap = TOK / 4 < 16 ? 16 : TOK / 4;
-    const int want = ((tok_tile + 63) / 64) * 16;
+  {  // the tile's share of one drain warp rounded up to 16 columns, at most a drain warp's register capacity
+    const int cap = TOK / kDW < 16 ? 16 : TOK / kDW;
+    const int want = ((tok_tile + 16 * kDW - 1) / (16 * kDW)) * 16;
     p.slice_cols = want < cap ? want : cap;
     p.mma_split = (a.K + kBlockK - 1) / kBlockK >= 2 ? 2 : 1;
     if (a.codes_int4_range) {
@@ -1085,7 +1235,7 @@ int launch_variant(const GemmArgs& a, int tok_tile, cudaStream_t stream, long lo
       launch_regs[dev] = attr.numRegs;
     }
     const int regs = (dev >= 0 && dev < 64) ? launch_regs[dev] : 0;
-    if (regs * kThreads < register_pool_needed(kSplit && TOK == 128)) return SQ_ERR_DRIVER;
+    if (regs * kThreads < register_pool_needed(kSplit && TOK == 128, kDW)) return SQ_ERR_DRIVER;
   }
   cudaError_t err;
   if (a.after_prepass) {
@@ -1123,6 +1273,12 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
   }
   const bool whole_chunks = TOK == 128 && kGroup && eo && !dump && ((a.K / kBlockK) & 7) == 0 && (a.K % kBlockK) == 0 &&
                             (reinterpret_cast<uintptr_t>(a.w_scales) & 15u) == 0;
+  static const int drain_warps_env = [] { const char* e = getenv("SQ_TC_DW"); return e != nullptr ? atoi(e) : 2; }();
+  const int drain_warps = a.gate == nullptr && a.residual == nullptr ? drain_warps_env : 4;  // the deferred finalize has no fused forms
+  if (a.weights_prepacked && whole_chunks && drain_warps == 2) {
+    return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, true, false, false, kGroup, kGroup ? 2 : 4>(a, tok_tile, stream)
+                : launch_variant<128, kGroup, true, false, __half, false, true, false, false, kGroup, kGroup ? 2 : 4>(a, tok_tile, stream);
+  }
   if (a.weights_prepacked && whole_chunks) {
     return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, true, false, false, kGroup>(a, tok_tile, stream)
                 : launch_variant<128, kGroup, true, false, __half, false, true, false, false, kGroup>(a, tok_tile, stream);
@@ -1138,6 +1294,10 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
     if (pick_splits(tok_tile, tiles, static_cast<int>((a.K + kBlockK - 1) / kBlockK), sm_count(), a.split_workspace_bytes) >= 2)
       return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, false, true>(a, tok_tile, stream)
                   : launch_variant<128, kGroup, true, false, __half, false, false, false, true>(a, tok_tile, stream);
+  }
+  if (whole_chunks && drain_warps == 2) {
+    return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, false, false, kGroup, kGroup ? 2 : 4>(a, tok_tile, stream)
+                : launch_variant<128, kGroup, true, false, __half, false, false, false, false, kGroup, kGroup ? 2 : 4>(a, tok_tile, stream);
   }
   if (whole_chunks) {
     // whole chunks of eight group scales per tile, no K split: the variant with the ring position unrolled
