@@ -96,7 +96,8 @@ __host__ __device__ constexpr int stages_for(int tok) {
 }
 __host__ __device__ constexpr uint32_t stage_bytes(int tok) { return kWBytes + tok * kBlockK + kPackedBytes; }
 __host__ __device__ constexpr uint32_t smem_bytes_for(int tok) {
-  return stages_for(tok) * stage_bytes(tok) + kConstTileBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  return stages_for(tok) * stage_bytes(tok) + kConstTileBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+         2048 /*row-scale tables of the two-warp drain*/;
 }
 
 struct TcParams {
@@ -181,6 +182,12 @@ __device__ __forceinline__ void report_timeout(int* status, volatile int* abort_
   atomicCAS(status, 0, code);
 }
 
+// Timeline capture inside the static drain: thread 256 (lane 0 of the first drain warp) of thread block 0 stamps the SM clock;
+// `tl` is null in every launch but sq_gemm_timeline's.
+__device__ __forceinline__ void stamp_drain(long long* tl, int role, uint32_t slot) {
+  if (tl != nullptr && threadIdx.x == 256 && slot < 512u) tl[role * 512 + slot] = clock64();
+}
+
 // One group of the drain (group form, chunked scales, no K split) with its place E in the chunk of eight group
 // scales - and with it its place E mod 4 in the accumulator ring - a compile-time constant: barrier addresses, TMEM
 // columns, the ring's phase and the position of the scale inside the chunk then cost no instructions.  `g` is the
@@ -191,11 +198,14 @@ __device__ __forceinline__ bool drain_group_static(uint32_t bar_acc_full, uint32
                                                    uint32_t phase, volatile int* abort_flag, int lane,
                                                    bool& acc_ready, uint4& chunk, uint4& chunk_next,
                                                    const unsigned short* my_scales, int groups, int g,
-                                                   float offset_float, float& offset_sum, uint64_t (&sums2)[kCols / 2]) {
+                                                   float offset_float, float& offset_sum, uint64_t (&sums2)[kCols / 2],
+                                                   long long* tl = nullptr, uint32_t slot0 = 0) {
   constexpr uint32_t POS = E & 3u;
   const uint32_t my_phase = E < 4u ? phase : phase ^ 1u;
+  stamp_drain(tl, 10, slot0 + E);
   if (!acc_ready && !mbar_wait_bounded(bar_acc_full + 8 * POS, my_phase, abort_flag, 1000ull * 1000ull * 1000ull)) return false;
   tc_fence_after_sync();
+  stamp_drain(tl, 5, slot0 + E);
   uint32_t r[kCols];
   tmem_ld_chunk(tmem_slice + POS * 128u, r);
   // the next group's barrier is probed under the load (a probe takes over a hundred cycles to answer)
@@ -213,53 +223,97 @@ __device__ __forceinline__ bool drain_group_static(uint32_t bar_acc_full, uint32
   tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) mbar_arrive(bar_acc_empty + 8 * POS);
+  stamp_drain(tl, 6, slot0 + E);
   const uint64_t scale2 = pack2(scale, scale);
 #pragma unroll
   for (int i = 0; i < kCols; i += 2) ffma2(sums2[i / 2], r[i], r[i + 1], scale2);
+  stamp_drain(tl, 7, slot0 + E);
   return true;
 }
 
-// The finished sums of a tile that wait for their finalize (two-warp drain): columns [kFirst, kFirst + kCount) of a
-// drain warp's 64 get their row scale (by shuffle from the lane that fetched it), bias and cast, and are stored.
-// `cols`: how many of the warp's columns are real tokens (0: nothing is pending, or this lane's channel does not exist);
-// the shuffles run in every lane.  The arithmetic is the finalize of the four-warp drain, operation for operation.
+// Two-warp drain: the results of a tile that wait to be stored.  When a tile's last group is done its 64 sums per
+// lane get their row scale, bias and cast at once (packed arithmetic, the row scales read four at a time from a
+// table the warp keeps in shared memory) and are kept as 32 words of two 16-bit results; the stores - a 64-byte run
+// per column and warp - then go out eight columns at a time under the accumulator loads of the next tile's first
+// eight groups, instead of holding up the accumulator ring between the tiles.
+// `cols`: how many of the warp's columns are real tokens (0: nothing is pending, or this lane's channel does not exist).
 template <typename OutT>
 struct PendingTile {
-  uint64_t sums2[32];
-  float offset_sum;
-  float rs[2];
-  float bias;
-  OutT* out;  // row of the slice's first token, this lane's channel
+  uint32_t pairs[32];  // columns 2i (low half) and 2i + 1 (high half)
+  OutT* out;           // row of the slice's first token, this lane's channel
   int cols;
 };
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_out2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack_out2<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_out2<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t c;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(c) : "l"(a), "l"(b));
+  return c;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t c;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(c) : "l"(a), "l"(b));
+  return c;
+}
+// (sum - offset_sum) * row scale (+ bias), each operation rounded as in the four-warp drain's finalize; rs_table: this
+// warp's 64 row scales in shared memory (byte address), written by the warp itself just before
+template <typename OutT>
+__device__ __forceinline__ void finish_tile(PendingTile<OutT>& t, const uint64_t (&sums2)[32], float offset_sum, float bias,
+                                            bool has_bias, uint32_t rs_table) {
+  const uint64_t minus_offset = pack2(-offset_sum, -offset_sum);
+  const uint64_t bias2 = pack2(bias, bias);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float r0, r1, r2, r3;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r0), "=f"(r1), "=f"(r2), "=f"(r3) : "r"(rs_table + 16 * j));
+    uint64_t a = mul2(add2(sums2[2 * j], minus_offset), pack2(r0, r1));
+    uint64_t b = mul2(add2(sums2[2 * j + 1], minus_offset), pack2(r2, r3));
+    if (has_bias) {
+      a = add2(a, bias2);
+      b = add2(b, bias2);
+    }
+    const float2 fa = unpack2(a), fb = unpack2(b);
+    t.pairs[2 * j] = pack_out2<OutT>(fa.x, fa.y);
+    t.pairs[2 * j + 1] = pack_out2<OutT>(fb.x, fb.y);
+  }
+}
+// the stores of columns [kFirst, kFirst + kCount) of the pending tile
 template <int kFirst, int kCount, typename OutT>
-__device__ __forceinline__ void finalize_pending(const PendingTile<OutT>& t, bool has_bias, int64_t out_ld) {
+__device__ __forceinline__ void store_pending(const PendingTile<OutT>& t, int64_t out_ld) {
+  unsigned short* out = reinterpret_cast<unsigned short*>(t.out);
 #pragma unroll
   for (int i = kFirst; i < kFirst + kCount; ++i) {
-    const float rs = __shfl_sync(0xffffffffu, t.rs[i >> 5], i & 31);
-    const float2 pair = unpack2(t.sums2[i / 2]);
-    float y = __fmul_rn(__fsub_rn((i & 1) != 0 ? pair.y : pair.x, t.offset_sum), rs);
-    if (has_bias) y = __fadd_rn(y, t.bias);
-    if (i < t.cols) t.out[i * out_ld] = from_float<OutT>(y);
+    const uint32_t word = t.pairs[i / 2];
+    if (i < t.cols) out[i * out_ld] = static_cast<unsigned short>((i & 1) != 0 ? word >> 16 : word & 0xFFFFu);
   }
 }
 
-// A group of a tile's first round in the two-warp drain: as drain_group_static, but the 64 columns come as two loads
-// of 32 (the registers of a full-width load are taken by the pending sums), and eight columns of the pending tile
-// are finalized while those loads are in flight: the finalize of tile t runs under the first eight groups of tile
-// t + 1 instead of holding up the accumulator ring between the tiles.
+// A group of a tile's first round in the two-warp drain: drain_group_static with the stores of eight columns of the
+// pending tile issued while the accumulator load is in flight.
 template <uint32_t E, typename OutT>
 __device__ __forceinline__ bool drain_group_first(uint32_t bar_acc_full, uint32_t bar_acc_empty, uint32_t tmem_slice,
                                                   uint32_t phase, volatile int* abort_flag, int lane, bool& acc_ready,
                                                   uint4& chunk, uint4& chunk_next, const unsigned short* my_scales,
                                                   int groups, int g, float offset_float, float& offset_sum,
-                                                  uint64_t (&sums2)[32], const PendingTile<OutT>& pending, bool has_bias,
-                                                  int64_t out_ld) {
+                                                  uint64_t (&sums2)[32], const PendingTile<OutT>& pending, int64_t out_ld,
+                                                  long long* tl = nullptr, uint32_t slot0 = 0) {
   constexpr uint32_t POS = E & 3u;
   const uint32_t my_phase = E < 4u ? phase : phase ^ 1u;
+  stamp_drain(tl, 10, slot0 + E);
   if (!acc_ready && !mbar_wait_bounded(bar_acc_full + 8 * POS, my_phase, abort_flag, 1000ull * 1000ull * 1000ull)) return false;
   tc_fence_after_sync();
-  uint32_t r[32];
+  stamp_drain(tl, 5, slot0 + E);
+  uint32_t r[64];
   tmem_ld_chunk(tmem_slice + POS * 128u, r);
   acc_ready = mbar_test_wait(bar_acc_full + 8 * ((POS + 1u) & 3u), POS == 3u ? my_phase ^ 1u : my_phase);
   const uint32_t word = E < 2u ? chunk.x : E < 4u ? chunk.y : E < 6u ? chunk.z : chunk.w;
@@ -271,19 +325,16 @@ __device__ __forceinline__ bool drain_group_first(uint32_t bar_acc_full, uint32_
     if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
   }
   offset_sum = fmaf(offset_float, scale, offset_sum);
-  const uint64_t scale2 = pack2(scale, scale);
-  finalize_pending<8 * E, 4, OutT>(pending, has_bias, out_ld);
-  tmem_wait_ld();
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) ffma2(sums2[i / 2], r[i], r[i + 1], scale2);
-  tmem_ld_chunk(tmem_slice + POS * 128u + 32u, r);
-  finalize_pending<8 * E + 4, 4, OutT>(pending, has_bias, out_ld);
+  store_pending<8 * E, 8, OutT>(pending, out_ld);
   tmem_wait_ld();
   tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) mbar_arrive(bar_acc_empty + 8 * POS);
+  stamp_drain(tl, 6, slot0 + E);
+  const uint64_t scale2 = pack2(scale, scale);
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) ffma2(sums2[16 + i / 2], r[i], r[i + 1], scale2);
+  for (int i = 0; i < 64; i += 2) ffma2(sums2[i / 2], r[i], r[i + 1], scale2);
+  stamp_drain(tl, 7, slot0 + E);
   return true;
 }
 
@@ -452,6 +503,78 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       // own accumulator), so the barrier round trips of one group overlap the issue of the next two.
       // Channel mode: warp 1 alone, because all K blocks of a tile add into one accumulator in order.
       const uint32_t mine = static_cast<uint32_t>(warp - 1);
+      if constexpr (kGroup) {
+        // Group form.  An issuer's own chain per group - two barrier round trips, the issue, the loop around it - has
+        // three group times to finish in, and on a scheduler it shares with drain warps in long runs of arithmetic
+        // every instruction of it waits its turn: the loop steps from one of its groups straight to the next, with
+        // the group's stage and accumulator (and their barrier phases) as running values, and issues the offset MMA,
+        // the four MMAs and both commits in one elected region.
+        uint32_t git = mine;                 // this issuer's next group, counted over all work items of the thread block
+        uint32_t s = mine, phase = 0;        // its stage of the load ring (mine < 3 <= S)
+        uint32_t buf = mine, aphase = 0;     // its accumulator of the ring of four
+        uint32_t base = 0;                   // groups of the items before this one
+        bool ok = true;
+        const uint64_t desc_c = umma_desc_k128(c_tile);
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+          int tile, kb0, kb1;
+          item_range(item, tile, kb0, kb1);
+          const uint32_t end = base + static_cast<uint32_t>(kb1 - kb0);
+          if (git < end) {
+            const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
+            const int64_t left = p.M - tok0;
+            const int tok_count = left < p.tok_tile ? static_cast<int>(left) : p.tok_tile;
+            const uint32_t umma_n = static_cast<uint32_t>((tok_count + 15) & ~15);
+            const uint32_t idesc = umma_idesc_i8(kBlockCh, umma_n);
+            // codes of any int8 value: ONE unsigned x unsigned MMA of 0xFF bytes adds 32 * 255 * 255, which covers
+            // the most negative group sum (16 * 8 * 127 * 128); codes within [-8, 7]: one signed MMA of 0x40 bytes
+            const uint32_t idesc_offset = p.offset_unsigned != 0 ? umma_idesc_u8(kBlockCh, umma_n) : idesc;
+            for (; git < end; git += 3) {
+              if (lane == 0) stamp(kTrIssuerWaits, git);
+              if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, aphase, abort_flag, kWaitLimitNs)) {
+                if (lane == 0) report_timeout(p.status, abort_flag, 9002);
+                ok = false;
+                break;
+              }
+              if (lane == 0) stamp(kTrMmaAccFree, git);
+              if (!mbar_wait_bounded(bar_wfull + 8 * s, phase, abort_flag, kWaitLimitNs)) {
+                if (lane == 0) report_timeout(p.status, abort_flag, 9003);
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              if (lane == 0) stamp(kTrMmaIssue, git);
+              if (elect_one()) {
+                const uint32_t tmem_d = tmem_base + buf * kBufStride;
+                // the offset MMA starts the accumulator at a positive value (no operand from the pipeline)
+                umma_i8(tmem_d, desc_c, desc_c, idesc_offset, 0u);
+                const uint64_t desc_a = umma_desc_k128(w_ring + s * kWBytes);
+                const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
+#pragma unroll
+                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                  // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in the (address >> 4) field
+                  umma_i8(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, 1u);
+                }
+                umma_commit(bar_empty + 8 * s);        // frees the stage when these MMAs retire
+                umma_commit(bar_acc_full + 8 * buf);   // and hands the accumulator to the drain
+              }
+              __syncwarp();
+              if (lane == 0) stamp(kTrMmaCommitted, git);
+              s += 3;
+              if (s >= static_cast<uint32_t>(S)) {
+                s -= S;
+                phase ^= 1u;
+              }
+              if (buf == 0) {
+                buf = 3;
+              } else {
+                buf -= 1;
+                aphase ^= 1u;
+              }
+            }
+          }
+          base = end;
+        }
+      } else {
       uint32_t it = 0, git = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
@@ -485,7 +608,11 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           }
           if (lane == 0) stamp(kTrMmaAccFree, git);
           const uint32_t tmem_d = tmem_base + buf * kBufStride;
+#ifdef SQ_TC_NO_OFFSET
+          if (false) {
+#else
           if (kGroup) {
+#endif
             // the offset MMAs need no operand from the pipeline: they start the accumulator at a positive value
             tc_fence_after_sync();
             if (elect_one()) {
@@ -511,7 +638,11 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
               const uint64_t desc_b = umma_desc_k128(x_ring + s * kXBytes);
 #pragma unroll
               for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+#ifdef SQ_TC_NO_OFFSET
+                const uint32_t accumulate = k > 0 ? 1u : 0u;
+#else
                 const uint32_t accumulate = (kGroup || static_cast<uint32_t>(kb) >= split || k > 0) ? 1u : 0u;
+#endif
                 // advancing K by 32 bytes inside the 128-byte swizzle row: +2 in the (address >> 4) field
                 umma_i8(tmem_d, desc_a + 2 * k, desc_b + 2 * k, idesc, accumulate);
               }
@@ -524,6 +655,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           }
           if (lane == 0) stamp(kTrMmaCommitted, git);
         }
+      }
       }
     }
   } else if (warp < 8) {
@@ -632,12 +764,13 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     // two-warp drain: the sums of the tile before, finalized under the first groups of the tile in hand
     PendingTile<OutT> pending;
     pending.cols = 0;
-    pending.offset_sum = 0.0f;
-    pending.rs[0] = pending.rs[1] = 0.0f;
-    pending.bias = 0.0f;
     pending.out = static_cast<OutT*>(p.out);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) pending.sums2[i] = 0ull;
+    for (int i = 0; i < 32; ++i) pending.pairs[i] = 0u;
+    const uint32_t rs_table = bars + 256 + static_cast<uint32_t>(dwarp & 7) * 256u;  // this warp's 64 row scales
+    // the first two chunks of group scales of the coming tile, requested a tile ahead (a global load in front of a
+    // tile's first group would hold up every role of the pipeline)
+    uint4 ahead_chunk = make_uint4(0u, 0u, 0u, 0u), ahead_chunk_next = make_uint4(0u, 0u, 0u, 0u);
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       int tile, kb0, kb1;
       item_range(item, tile, kb0, kb1);
@@ -683,7 +816,10 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       uint4 chunk = make_uint4(0u, 0u, 0u, 0u), chunk_next = make_uint4(0u, 0u, 0u, 0u);
       unsigned short raw_a = 0, raw_b = 0;
       if (kGroup) {
-        if (scale_vectors) {
+        if (kStatic && kDW == 2 && item != static_cast<int>(blockIdx.x)) {
+          chunk = ahead_chunk;
+          chunk_next = ahead_chunk_next;
+        } else if (scale_vectors) {
           chunk = __ldg(reinterpret_cast<const uint4*>(my_scales) + (g0 >> 3));
           if (8 * ((g0 >> 3) + 1) < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + (g0 >> 3) + 1);
           {
@@ -705,17 +841,26 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       }
 
       if constexpr (kStatic && kDW == 2) {
-        const bool has_bias_now = p.bias != nullptr;
+        long long* trace_to = kTrace && tracing ? p.timeline : nullptr;
+        {
+          // (past the last tile this reads the first tile's scales again: always a valid address, never used)
+          const int item_ahead = item + static_cast<int>(gridDim.x) < num_items ? item + static_cast<int>(gridDim.x) : 0;
+          const int64_t n_ahead = (item_ahead % p.ch_tiles) * kBlockCh + ch_in_tile;
+          const uint4* scales_ahead = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(scale_row) +
+                                                                     (n_ahead < p.N ? n_ahead : 0) * groups);
+          ahead_chunk = __ldg(scales_ahead);
+          ahead_chunk_next = __ldg(scales_ahead + (groups > 8 ? 1 : 0));
+        }
         if (my_cols > 0) {
           const uint32_t phase = (git >> 2) & 1u;
           const uint32_t tmem_slice = tmem_base + lane_addr + my_col0;
           int g = g0;
 #define SQ_DRAIN_FIRST(E)                                                                                               \
   drain_group_first<E, OutT>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready, chunk, chunk_next, \
-                             my_scales, groups, g, offset_float, offset_sum, sums2, pending, has_bias_now, p.out_ld)
+                             my_scales, groups, g, offset_float, offset_sum, sums2, pending, p.out_ld, trace_to, git)
 #define SQ_DRAIN_AT(E)                                                                                                   \
   drain_group_static<E, kCols>(bar_acc_full, bar_acc_empty, tmem_slice, phase, abort_flag, lane, acc_ready, chunk, chunk_next, \
-                               my_scales, groups, g, offset_float, offset_sum, sums2)
+                               my_scales, groups, g, offset_float, offset_sum, sums2, trace_to, git)
           ok = SQ_DRAIN_FIRST(0u) && SQ_DRAIN_FIRST(1u) && SQ_DRAIN_FIRST(2u) && SQ_DRAIN_FIRST(3u) && SQ_DRAIN_FIRST(4u) &&
                SQ_DRAIN_FIRST(5u) && SQ_DRAIN_FIRST(6u) && SQ_DRAIN_FIRST(7u);
           git += 8;
@@ -726,8 +871,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
 #undef SQ_DRAIN_AT
 #undef SQ_DRAIN_FIRST
         } else {
-          // no columns of this tile (past the last token): finalize what is pending, keep the hand-over going
-          finalize_pending<0, 64, OutT>(pending, has_bias_now, p.out_ld);
+          // no columns of this tile (past the last token): store what is pending, keep the hand-over going
+          store_pending<0, 64, OutT>(pending, p.out_ld);
           for (int g = g0; g < g1 && ok; ++g, ++git) {
             const uint32_t buf = git & 3u;
             ok = mbar_wait_bounded(bar_acc_full + 8 * buf, (git >> 2) & 1u, abort_flag, kWaitLimitNs);
@@ -741,13 +886,12 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           if (lane == 0) report_timeout(p.status, abort_flag, 9005);
           break;
         }
-        // this tile's sums now wait for their turn
-#pragma unroll
-        for (int i = 0; i < 32; ++i) pending.sums2[i] = sums2[i];
-        pending.offset_sum = offset_sum;
-        pending.rs[0] = my_rs[0];
-        pending.rs[1] = my_rs[kCols > 32 ? 1 : 0];
-        pending.bias = bias;
+        // this tile's results: scaled and cast now, stored under the next tile's first groups
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(rs_table + 4 * lane), "f"(my_rs[0]) : "memory");
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(rs_table + 128 + 4 * lane), "f"(my_rs[kCols > 32 ? 1 : 0]) : "memory");
+        __syncwarp();
+        finish_tile<OutT>(pending, sums2, offset_sum, bias, p.bias != nullptr, rs_table);
+        __syncwarp();
         pending.out = static_cast<OutT*>(p.out) + m0 * p.out_ld + p.out_col0 + (n_ok ? n : 0);
         pending.cols = n_ok ? my_cols : 0;
         continue;
@@ -1054,7 +1198,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       if (threadIdx.x == 256) stamp(kTrTileEnds, 2 * (git / groups) - 1);
     }
     if constexpr (kStatic && kDW == 2) {
-      if (ok) finalize_pending<0, 64, OutT>(pending, p.bias != nullptr, p.out_ld);
+      if (ok) store_pending<0, 64, OutT>(pending, p.out_ld);
     }
   }
 
@@ -1416,6 +1560,9 @@ int launch_gemm_timeline(const GemmArgs& a, long long* timeline, cudaStream_t st
   const int ch_tiles = static_cast<int>((a.N + kBlockCh - 1) / kBlockCh);
   int t = pick_tok_tile(a.M, ch_tiles, static_cast<int>((a.K + kBlockK - 1) / kBlockK), sm_count(), 0);
   if (t <= 64) t = 128;
+  if (((a.K / kBlockK) & 7) == 0 && (a.K % kBlockK) == 0 && (reinterpret_cast<uintptr_t>(a.w_scales) & 15u) == 0 &&
+      a.gate == nullptr && a.residual == nullptr)  // the form large problems run: two-warp drain, static ring
+    return launch_variant<128, true, true, false, __nv_bfloat16, true, false, false, false, true, 2>(a, t, stream, timeline);
   return launch_variant<128, true, true, false, __nv_bfloat16, true>(a, t, stream, timeline);
 }
 
