@@ -213,16 +213,17 @@ __device__ __forceinline__ bool drain_group_static(uint32_t bar_acc_full, uint32
   const uint32_t word = E < 2u ? chunk.x : E < 4u ? chunk.y : E < 6u ? chunk.z : chunk.w;
   const __half2 pair = *reinterpret_cast<const __half2*>(&word);
   const float scale = ((E & 1u) != 0u ? __high2float(pair) : __low2float(pair)) * 7.922816251426434e28f;  // 2^96 (kScaleUp)
-  if (E == 7u) {  // the chunk is used up: the next one takes its place, the one after that is requested
-    chunk = chunk_next;
-    const int c2 = (g >> 3) + 2;
-    if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
-  }
   offset_sum = fmaf(offset_float, scale, offset_sum);
   tmem_wait_ld();
   tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) mbar_arrive(bar_acc_empty + 8 * POS);
+  // (after the hand-back: the arrive is a release, and a global load or store issued before it would make it wait)
+  if (E == 7u) {  // the chunk is used up: the next one takes its place, the one after that is requested
+    chunk = chunk_next;
+    const int c2 = (g >> 3) + 2;
+    if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+  }
   stamp_drain(tl, 6, slot0 + E);
   const uint64_t scale2 = pack2(scale, scale);
 #pragma unroll
@@ -299,7 +300,7 @@ __device__ __forceinline__ void store_pending(const PendingTile<OutT>& t, int64_
 }
 
 // A group of a tile's first round in the two-warp drain: drain_group_static with the stores of eight columns of the
-// pending tile issued while the accumulator load is in flight.
+// pending tile issued after the accumulator's hand-back, in front of the arithmetic.
 template <uint32_t E, typename OutT>
 __device__ __forceinline__ bool drain_group_first(uint32_t bar_acc_full, uint32_t bar_acc_empty, uint32_t tmem_slice,
                                                   uint32_t phase, volatile int* abort_flag, int lane, bool& acc_ready,
@@ -319,17 +320,18 @@ __device__ __forceinline__ bool drain_group_first(uint32_t bar_acc_full, uint32_
   const uint32_t word = E < 2u ? chunk.x : E < 4u ? chunk.y : E < 6u ? chunk.z : chunk.w;
   const __half2 pair = *reinterpret_cast<const __half2*>(&word);
   const float scale = ((E & 1u) != 0u ? __high2float(pair) : __low2float(pair)) * 7.922816251426434e28f;  // 2^96 (kScaleUp)
+  offset_sum = fmaf(offset_float, scale, offset_sum);
+  tmem_wait_ld();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_acc_empty + 8 * POS);
+  // (after the hand-back: the arrive is a release, and a global load or store issued before it would make it wait)
   if (E == 7u) {
     chunk = chunk_next;
     const int c2 = (g >> 3) + 2;
     if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
   }
-  offset_sum = fmaf(offset_float, scale, offset_sum);
   store_pending<8 * E, 8, OutT>(pending, out_ld);
-  tmem_wait_ld();
-  tc_fence_before_sync();
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar_acc_empty + 8 * POS);
   stamp_drain(tl, 6, slot0 + E);
   const uint64_t scale2 = pack2(scale, scale);
 #pragma unroll
@@ -851,6 +853,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           ahead_chunk = __ldg(scales_ahead);
           ahead_chunk_next = __ldg(scales_ahead + (groups > 8 ? 1 : 0));
         }
+        stamp_drain(trace_to, kTrTileEnds, 4 * (git / groups) + 2);  // the tile's head is done
         if (my_cols > 0) {
           const uint32_t phase = (git >> 2) & 1u;
           const uint32_t tmem_slice = tmem_base + lane_addr + my_col0;
@@ -887,6 +890,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           break;
         }
         // this tile's results: scaled and cast now, stored under the next tile's first groups
+        stamp_drain(trace_to, kTrTileEnds, 4 * (git / groups) - 4);  // the last group is done
         asm volatile("st.shared.f32 [%0], %1;" ::"r"(rs_table + 4 * lane), "f"(my_rs[0]) : "memory");
         asm volatile("st.shared.f32 [%0], %1;" ::"r"(rs_table + 128 + 4 * lane), "f"(my_rs[kCols > 32 ? 1 : 0]) : "memory");
         __syncwarp();
@@ -894,6 +898,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
         __syncwarp();
         pending.out = static_cast<OutT*>(p.out) + m0 * p.out_ld + p.out_col0 + (n_ok ? n : 0);
         pending.cols = n_ok ? my_cols : 0;
+        stamp_drain(trace_to, kTrTileEnds, 4 * (git / groups) - 3);  // scaled and cast
         continue;
       } else if constexpr (kStatic) {
         // The launcher picks this variant when every tile has a multiple of eight groups in chunked scales and K is
@@ -974,9 +979,7 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             // funnel shifts instead of picking a half out of four registers by the group index)
             raw = static_cast<unsigned short>(chunk.x & 0xFFFFu);
             if ((g & 7) == 7) {
-              chunk = chunk_next;
-              const int c2 = (g >> 3) + 2;
-              if (8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+              chunk = chunk_next;  // (the chunk after that is requested below, after the hand-back)
             } else {
               chunk.x = __funnelshift_r(chunk.x, chunk.y, 16);
               chunk.y = __funnelshift_r(chunk.y, chunk.z, 16);
@@ -985,10 +988,6 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
             }
           } else {
             raw = (g & 1) == 0 ? raw_a : raw_b;
-            if (g + 2 < groups) {
-              const unsigned short ahead = __ldg(my_scales + g + 2);
-              if ((g & 1) == 0) raw_a = ahead; else raw_b = ahead;
-            }
           }
           scale = __half2float(__ushort_as_half(raw)) * kScaleUp;
           offset_sum = fmaf(offset_float, scale, offset_sum);
@@ -1002,6 +1001,17 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
           if (!kGroup) mbar_arrive(bar_acc_empty + 8 * (buf + 1));  // kept in step even when unused
         }
         if (threadIdx.x == 256) stamp(kTrDrainRelease, git);
+        if (kGroup) {
+          // the coming scales are requested after the hand-back: the arrive is a release, and a global load issued
+          // before it would make it wait for the load
+          if (scale_vectors) {
+            const int c2 = (g >> 3) + 2;
+            if ((g & 7) == 7 && 8 * c2 < groups) chunk_next = __ldg(reinterpret_cast<const uint4*>(my_scales) + c2);
+          } else if (g + 2 < groups) {
+            const unsigned short ahead = __ldg(my_scales + g + 2);
+            if ((g & 1) == 0) raw_a = ahead; else raw_b = ahead;
+          }
+        }
         if (my_cols > 0) {
           const uint64_t scale2 = pack2(scale, scale);
 #pragma unroll
