@@ -87,6 +87,9 @@ constexpr int kNumConverterWarps = 4;
 #ifndef SQ_TC_STAGES128
 #define SQ_TC_STAGES128 5
 #endif
+// Four stages measured 3-7 % slower than five; a three-stage build ended in a launch failure in the per-channel
+// prepacked form and is refused here (the cause was not found by reading the code, and it was not run again).
+static_assert(SQ_TC_STAGES128 >= 4 && SQ_TC_STAGES128 <= 5, "load stages of the 128-token kernel");
 #ifndef SQ_TC_EARLY_PROBE
 #define SQ_TC_EARLY_PROBE 1
 #endif
@@ -773,12 +776,20 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
     // the first two chunks of group scales of the coming tile, requested a tile ahead (a global load in front of a
     // tile's first group would hold up every role of the pipeline)
     uint4 ahead_chunk = make_uint4(0u, 0u, 0u, 0u), ahead_chunk_next = make_uint4(0u, 0u, 0u, 0u);
+    // without a K split a work item is a tile and the next one lies gridDim.x tiles on: channel tile and token tile
+    // as running values (two integer divisions per tile sit in front of the tile's first group otherwise)
+    int ch_idx = static_cast<int>(blockIdx.x) % p.ch_tiles, tok_idx = static_cast<int>(blockIdx.x) / p.ch_tiles;
+    const int step_ch = static_cast<int>(gridDim.x) % p.ch_tiles, step_tok = static_cast<int>(gridDim.x) / p.ch_tiles;
     for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       int tile, kb0, kb1;
       item_range(item, tile, kb0, kb1);
       const int g0 = kGroup ? kb0 : 0, g1 = kGroup ? kb1 : 1;  // this item's groups
-      const int ch0 = (tile % p.ch_tiles) * kBlockCh;
-      const int tok0 = (tile / p.ch_tiles) * p.tok_tile;
+      const int ch0 = (kSplitK ? tile % p.ch_tiles : ch_idx) * kBlockCh;
+      const int tok0 = (kSplitK ? tile / p.ch_tiles : tok_idx) * p.tok_tile;
+      // the coming tile's coordinates
+      const int ch_ahead = ch_idx + step_ch >= p.ch_tiles ? ch_idx + step_ch - p.ch_tiles : ch_idx + step_ch;
+      tok_idx += step_tok + (ch_idx + step_ch >= p.ch_tiles ? 1 : 0);
+      ch_idx = ch_ahead;
       const int64_t left = p.M - tok0;
       const int tok_count = left < p.tok_tile ? static_cast<int>(left) : p.tok_tile;
       const int my_cols = min(max(tok_count - my_col0, 0), p.slice_cols);  // real tokens in my slice
@@ -845,9 +856,8 @@ sq_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_c
       if constexpr (kStatic && kDW == 2) {
         long long* trace_to = kTrace && tracing ? p.timeline : nullptr;
         {
-          // (past the last tile this reads the first tile's scales again: always a valid address, never used)
-          const int item_ahead = item + static_cast<int>(gridDim.x) < num_items ? item + static_cast<int>(gridDim.x) : 0;
-          const int64_t n_ahead = (item_ahead % p.ch_tiles) * kBlockCh + ch_in_tile;
+          // (past the last tile this reads some tile's scales again: always a valid address, never used)
+          const int64_t n_ahead = ch_ahead * kBlockCh + ch_in_tile;
           const uint4* scales_ahead = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(scale_row) +
                                                                      (n_ahead < p.N ? n_ahead : 0) * groups);
           ahead_chunk = __ldg(scales_ahead);

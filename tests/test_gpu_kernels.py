@@ -315,6 +315,45 @@ def test_channel_form_split_along_k_is_exact(native, oracle, m, k, n):
     assert native.device_status() == 0
 
 
+@pytest.mark.parametrize("m,k,n", [(1100, 1024, 200), (1190, 2048, 392), (180, 3072, 136), (40000, 1024, 136)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_static_two_warp_drain_edges(native, oracle, m, k, n, dtype, with_bias):
+    """The form large problems run (K a multiple of 1024: whole chunks of eight group scales; drain warps of 64 token
+    columns; a tile's results stored under the next tile's first groups) at its edges: a last token tile that
+    leaves one drain warp of a lane quarter with a few columns or with none, channel counts that are no multiple of
+    the 128-channel tile, one round per tile (K = 1024) and several, both output types, with and without bias,
+    packed and prepacked weights, and more tiles per thread block than the pending results could be mixed up in
+    (m = 40000: 313 token tiles x 2 channel tiles on 148 thread blocks).  The output must equal, bit for bit, that of
+    the generic kernel (the one that also dumps its accumulators, which are checked against exact integer sums)."""
+    gen = torch.Generator().manual_seed(m + k + n)
+    codes = torch.randint(-7, 8, (m, k), generator=gen, dtype=torch.int8)
+    qweight = torch.randint(-8, 8, (n, k), generator=gen, dtype=torch.int8)
+    wscales = (torch.rand(n, k // 128, generator=gen) * 0.01 + 0.001).half().cuda()
+    row_scales = (torch.rand(m, generator=gen) + 0.5).cuda()
+    bias = (torch.randn(n, generator=gen) * 0.01).to(dtype).cuda() if with_bias else None
+    packed = oracle.pack_signed_int4(qweight).cuda()
+    dev_codes = even_odd(codes).cuda()
+    generic, acc = native.gemm(dev_codes, packed, wscales, row_scales, bias, out_dtype=dtype, want_accumulators=True,
+                               split=False)
+    rows = torch.arange(0, m, max(1, m // 40))
+    want_acc = torch.einsum("mgk,ngk->mng", codes[rows].view(len(rows), -1, 128).double(),
+                            qweight.view(n, -1, 128).double()).long()
+    assert torch.equal(acc[rows.cuda()].cpu().long(), want_acc)
+    del acc
+    for int4_range in (False, True):
+        static = native.gemm(dev_codes, packed, wscales, row_scales, bias, out_dtype=dtype, int4_range=int4_range,
+                             split=False)
+        if not int4_range:
+            assert torch.equal(static, generic)
+        else:  # another offset constant: the fp32 sums may round differently
+            assert rel_fro(static, generic) < 2e-3
+        pre = native.gemm(dev_codes, native.prepack_weights(packed), wscales, row_scales, bias, out_dtype=dtype,
+                          int4_range=int4_range, split=False)
+        assert torch.equal(pre, static)
+    assert native.device_status() == 0
+
+
 @pytest.mark.parametrize("m,k,n", [(300, 3072, 384), (17, 256, 136), (520, 1024, 128), (2048, 1024, 512)])
 @pytest.mark.parametrize("group", [True, False])
 def test_prepacked_weights_give_the_same_bits(native, oracle, m, k, n, group):
