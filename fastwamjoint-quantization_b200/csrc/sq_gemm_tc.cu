@@ -5,7 +5,7 @@
 // output channel, so the per-group weight scale is a per-thread scalar when the accumulator is
 // drained, and small token counts map to a small UMMA N instead of a wasted 128-row tile.
 //
-// Per CTA (persistent over tiles, 768 threads):
+// Per CTA (persistent over tiles; 768 threads, or 512 in the two-warp drain):
 //   warp 0        TMA producer: per 128-K block one box of packed int4 weights [128 ch x 64 B] and one
 //                 box of int8 activation codes [tokens x 128 B, 128-byte swizzle]
 //   warps 1-3     issue tcgen05.mma.kind::i8 (4 x K=32 per block) and commit to mbarriers; in the group form
@@ -15,10 +15,14 @@
 //                 operand tile (nibble v becomes the int8 value 16 v; the factor 1/16 is exact and is
 //                 folded into the scale).  With prepacked weights (kPre) the producer loads that tile itself
 //                 and these warps have nothing to do.
-//   warps 8-23    drain, four warps per TMEM lane quarter, each owning a slice of the token columns:
+//   warps 8-      drain, four warps per TMEM lane quarter (32 token columns each) or two (64 columns each):
 //                 tcgen05.ld the int32 accumulator of one weight group, hand the accumulator back, fold it
 //                 into fp32 sums in registers with the group scale; after the last group apply the row
 //                 scale, bias, gate and residual and store bf16/fp16
+// The drain loop comes in several forms (generic; ring and scale position unrolled, kStatic; two wide warps per lane
+// quarter with the stores of a tile deferred into the next, kDW = 2), each in a template instantiation of its own
+// that the launcher picks: two forms of the loop inside one kernel function made the compiler spill the accumulator
+// registers, which cost more than either form gains.
 // TMEM holds a ring of four accumulators, so the MMA warps run ahead of the drain.
 //
 // The group form is bound by the instructions the drain issues per accumulator element, so the integer to float
@@ -45,10 +49,10 @@ namespace {
 constexpr int kBlockCh = 128;  // output channels per tile = UMMA M = TMEM lanes
 constexpr int kBlockK = 128;   // int8 K elements per stage = one swizzle row = one weight group
 constexpr int kUmmaK = 32;     // K of one kind::i8 instruction
-// Register targets per role after setmaxnreg (control 24, unpack 40, drain 104).  setmaxnreg.inc only hands out
-// registers the CTA was launched with and waits for ever when the targets add up to more, so the launcher
-// checks this sum against (registers per thread at launch) x kThreads before every launch.
-// Registers per thread after the roles re-partition the CTA's allocation (setmaxnreg).  `wide_drain`: the variant of
+// Registers per thread after the roles re-partition the CTA's allocation (setmaxnreg).  setmaxnreg.inc only hands out
+// registers the CTA was launched with and waits for ever when the targets add up to more, so the launcher checks this
+// sum against (registers per thread at launch) x (threads) before every launch.  Control and unpack warps at 24 / 40
+// instead of 32 / 48 registers measured 8 % slower in the two-warp drain.  `wide_drain`: the variant of
 // the 128-token kernel that can split K keeps a few more values live in its drain loop and takes the registers for
 // them from the other roles.
 // `dw`: drain warps per TMEM lane quarter.  Four warps of 32 token columns each (768 threads, 80 registers per thread
