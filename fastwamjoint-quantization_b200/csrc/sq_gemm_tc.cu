@@ -1433,14 +1433,17 @@ int launch_tok(const GemmArgs& a, int tok_tile, cudaStream_t stream) {
 #define SQ_LAUNCH(EO, DUMP)                                                                          \
   (bf16 ? launch_variant<TOK, kGroup, EO, DUMP, __nv_bfloat16>(a, tok_tile, stream)          \
         : launch_variant<TOK, kGroup, EO, DUMP, __half>(a, tok_tile, stream))
+  const bool whole_chunks = TOK == 128 && kGroup && eo && !dump && ((a.K / kBlockK) & 7) == 0 && (a.K % kBlockK) == 0 &&
+                            (reinterpret_cast<uintptr_t>(a.w_scales) & 15u) == 0;
   if (a.n_more_outs > 0) {
     // channel-split form: the 128-token kernel only (a split over GPUs is for many tokens), even-odd codes, packed weights
     if (TOK != 128 || !eo || dump || a.weights_prepacked) return SQ_ERR_ENUM;
+    if (whole_chunks)  // the drain with the ring position unrolled (four warps per lane quarter: its finalize has the peer stores)
+      return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, true, false, kGroup>(a, tok_tile, stream)
+                  : launch_variant<128, kGroup, true, false, __half, false, false, true, false, kGroup>(a, tok_tile, stream);
     return bf16 ? launch_variant<128, kGroup, true, false, __nv_bfloat16, false, false, true>(a, tok_tile, stream)
                 : launch_variant<128, kGroup, true, false, __half, false, false, true>(a, tok_tile, stream);
   }
-  const bool whole_chunks = TOK == 128 && kGroup && eo && !dump && ((a.K / kBlockK) & 7) == 0 && (a.K % kBlockK) == 0 &&
-                            (reinterpret_cast<uintptr_t>(a.w_scales) & 15u) == 0;
   static const int drain_warps_env = [] { const char* e = getenv("SQ_TC_DW"); return e != nullptr ? atoi(e) : 2; }();
   const int drain_warps = a.gate == nullptr && a.residual == nullptr ? drain_warps_env : 4;  // the deferred finalize has no fused forms
   if (a.weights_prepacked && whole_chunks && drain_warps == 2) {
