@@ -144,7 +144,7 @@ size_t sq_split_workspace_bytes(int64_t M);
  * matrix on the other GPUs, given as peer pointers (CUDA IPC or any other peer mapping).  The epilogue stores every
  * 64-byte run of a row to all of them, so the all-gather that would follow the GEMM (ncclAllGather plus a local
  * permute into the [M, out_ld] layout) is the GEMM's own NVLink traffic and overlaps its tensor-core work tile by
- * tile.  Plain stores only: no TMA and no multicast touches peer memory.  The caller orders the GPUs around the call
+ * tile.  Plain stores only: no TMA copy and no cluster-wide load touches peer memory.  The caller orders the GPUs around the call
  * (nobody may read a matrix before every GPU's kernel has finished; nobody may start the next call's stores
  * before every reader is done).  M >= 128; packed int4 weights; even-odd codes; bf16 or fp16 output.
  * The reference has no counterpart (it runs on one GPU). */
